@@ -1,0 +1,161 @@
+/*
+ * slidesparse_b200.h -- C ABI of the B200 (sm_100a) sparse W8A8 projection library.
+ *
+ * Every entry point takes plain pointers and sizes (no torch types), an explicit CUDA stream
+ * (a cudaStream_t passed as void*; NULL = legacy default stream) and returns 0 on success or a
+ * negative SS_E_* code; ss_last_error() gives the message of the calling thread's last failure.
+ * Device pointers must belong to the device that is current when the call is made.  Nothing here
+ * synchronises the stream or allocates device memory unless the comment of the entry says so.
+ *
+ * The comment above each declaration names the reference interface it replaces, as
+ * file:line inside the SlideSparse-Diffusion source tree.
+ *
+ * Formats shared by all entries (mode group l in {4,6,8} for 2:4 / 4:6 / 6:8):
+ *   valid = ceil(k/l) * (l/2-1) * 4      lifted K'        (packing.py:15-20)
+ *   pk    = ceil128(valid)                padded K'
+ *   pm    = ceil32(m), pn = ceil32(n)
+ *   q        int8  [pm, pk]   quantised, slide-expanded activations, rows m..pm-1 zero
+ *   sa       fp32  [pm]       per-token scales, rows m..pm-1 are 1.0
+ *   packed   int8  [pn, pk/2] 2:4-compressed weights, bit-identical to the reference's
+ *   metadata int32 [pn*pk/32] 4-bit index pairs, one nibble per quartet.  "raw" order is the
+ *            reference's pre-reorder array (row-major [pn, pk/32], quartet g of a row in word g/8
+ *            at bit 4*(g%8)).  The "b200" order, which the GEMM consumes, stores each block of
+ *            32 rows x 128 lifted columns as 512 contiguous bytes:
+ *              word(row r, raw column c) -> ((r/32)*(pk/128) + c/4)*128 + (r%32)*4 + c%4
+ */
+#ifndef SLIDESPARSE_B200_H
+#define SLIDESPARSE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SS_OK 0
+#define SS_E_ARG (-1)      /* contract violation: shape, alignment, null pointer, mode        */
+#define SS_E_CUDA (-2)     /* a CUDA runtime/driver call failed (message has the CUDA string) */
+#define SS_E_FORMAT (-3)   /* weight violates the (l-2):l or 2:4 structure                    */
+#define SS_E_HANDLE (-4)   /* unknown or released plan handle                                 */
+#define SS_E_DEVICE (-5)   /* a kernel reported a bounded wait that ran out                   */
+#define SS_E_LIMIT (-6)    /* size beyond a stated maximum of the entry point                 */
+
+/* Message for the calling thread's most recent non-zero return.  Never NULL. */
+const char* ss_last_error(void);
+
+/* Library/hardware facts.  out[0..7] = {abi version, compiled arch (100), device cc major,
+ * cc minor, SM count, max opt-in shared memory per block, TMEM columns per SM (512),
+ * GEMM kernel threads}.  Replaces the device gate and resource report of
+ * csrc/dualscale_sm80.cu:282-318 (configure).  device < 0 skips the device fields (CPU-only use). */
+int ss_query(int device, int64_t* out, int n_out);
+
+/* (valid, pk) for logical width k.  packing.py:15-20 (lifted_k, alignment 128). */
+int ss_lifted_k(int64_t k, int group, int64_t* valid, int64_t* pk);
+
+/* ---- offline packer, host side --------------------------------------------------------- */
+
+/* Exact (l-2):l -> overlapping 2:4 window expansion of an int8 weight [n,k] into [n,valid].
+ * packing.py:23-52 (slide_weight): increasing window, then increasing lane; SS_E_FORMAT if a
+ * group holds more than l-2 nonzeros. */
+int ss_slide_weight_cpu(const int8_t* qweight, int64_t n, int64_t k, int group, int8_t* lifted);
+
+/* 2:4 compression of a lifted weight [n,kl] (kl <= pk, pk % 128 == 0) into packed [pn,pk/2] and
+ * metadata.  meta_raw and meta_b200 may each be NULL.  csrc/dualscale_sm80.cu:254-274 (pack_cpu,
+ * values + raw words); the SM80 reorder of :275-278 is replaced by the b200 order above. */
+int ss_pack_cpu(const int8_t* lifted, int64_t n, int64_t kl, int64_t pk,
+                int8_t* packed, int32_t* meta_raw, int32_t* meta_b200);
+
+/* Convert metadata between the raw and the b200 order (to_b200 != 0: raw -> b200). */
+int ss_meta_convert(const int32_t* src, int32_t* dst, int64_t pn, int64_t pk, int to_b200);
+
+/* ---- offline packer, device side -------------------------------------------------------- */
+
+/* Per-output-channel symmetric INT8 grid of an already pruned weight: scale = 2*rowabsmax/255
+ * (1 if the row is all zero), q = clamp(rint(w/scale), -128, 127).  w is fp32 [n,k] on the
+ * device.  diffusion_research/reconstruction.py:41-53 (channel_scales, round_signed). */
+int ss_weight_grid_device(const float* w, int64_t n, int64_t k, int8_t* qweight, float* scales,
+                          void* stream);
+
+/* slide_weight + pack_cpu in one kernel on the device: qweight int8 [n,k] -> packed [pn,pk/2],
+ * metadata (b200 order).  status (device int32[1], zeroed by the caller) is set to 1 if any
+ * group violates the (l-2):l structure.  packing.py:23-52 + csrc/dualscale_sm80.cu:254-274. */
+int ss_pack_device(const int8_t* qweight, int64_t n, int64_t k, int group,
+                   int8_t* packed, int32_t* meta_b200, int32_t* status, void* stream);
+
+/* ---- front-end: dynamic per-token quantisation + slide expansion ------------------------ */
+
+/* x: BF16 [m,k], unit column stride, row stride x_row_stride elements.  Writes q [pm,pk] and
+ * sa [pm] in one pass.  csrc/projection_sm80.cu:8-88,99-120 (quant_lift, quantize);
+ * runtime.py:72-95 (quantize_lift). */
+int ss_quantize_lift(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k, int group,
+                     int8_t* q, float* sa, void* stream);
+
+/* ---- GEMM: 2:4 sparse INT8 tcgen05 contraction with fused dequant epilogue --------------- */
+
+/* out[m,n] (BF16, row stride out_row_stride elements) =
+ *   bf16( fma(float(acc), sa[tok]*sw[ch], bias[ch]) [+ float(addend[tok,ch])] ),
+ * acc = exact int32 dot of q[tok,:] with the decompressed weight row ch.  bias and addend may be
+ * NULL.  metadata is in b200 order.  csrc/dualscale_sm80.cu:320-398 (launch, run) and :72-187
+ * (scaled, DirectEpilogue). */
+int ss_gemm_run(const int8_t* q, const int8_t* packed, const int32_t* meta_b200,
+                const float* sa, const float* sw, const float* bias,
+                const void* addend_bf16, int64_t addend_row_stride,
+                void* out_bf16, int64_t out_row_stride,
+                int64_t m, int64_t n, int64_t pm, int64_t pn, int64_t pk, void* stream);
+
+/* Same contraction, raw int32 accumulators to acc[m,n] (row stride n).
+ * integrations/cachequant/csrc/native_sparse_int32_sm80.cu:38-62,112-133. */
+int ss_gemm_int32(const int8_t* q, const int8_t* packed, const int32_t* meta_b200,
+                  int32_t* acc, int64_t m, int64_t n, int64_t pm, int64_t pn, int64_t pk,
+                  void* stream);
+
+/* Front-end + GEMM in one call.  q_scratch [pm,pk] and sa_scratch [pm] are caller-provided
+ * device scratch.  csrc/projection_sm80.cu:142-148 (projection). */
+int ss_projection(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k, int group,
+                  const int8_t* packed, const int32_t* meta_b200,
+                  const float* sw, const float* bias,
+                  const void* addend_bf16, int64_t addend_row_stride,
+                  int64_t n, int64_t pn,
+                  int8_t* q_scratch, float* sa_scratch,
+                  void* out_bf16, int64_t out_row_stride, void* stream);
+
+/* ---- prepared plans (resident scratch, cached tensor maps) ------------------------------- */
+
+/* Creates a plan for a fixed (m,k,n,group) on the current device; allocates its resident
+ * q/sa scratch with cudaMalloc (the only allocating entry besides ss_plan_release's free).
+ * Weight/scale/bias pointers are re-read at every run, so callers may overwrite their contents.
+ * Returns 0 and the handle in *handle.  csrc/graph_projection.cuh:127-152 (prepare*). */
+int ss_plan_create(const int8_t* packed, const int32_t* meta_b200, const float* sw,
+                   const float* bias, int64_t k, int64_t m, int64_t n, int64_t pn, int group,
+                   int64_t* handle);
+
+/* Runs a plan.  On the stream that ran the plan last it uses the resident scratch; on another
+ * stream, or while that stream is being captured into a CUDA graph, the caller must pass
+ * scratch (q_scratch, sa_scratch) of the plan's size, else SS_E_ARG.
+ * csrc/graph_projection.cuh:92-125,153-158 (Plan::forward, run). */
+int ss_plan_run(int64_t handle, const void* x_bf16, int64_t x_row_stride,
+                int8_t* q_scratch, float* sa_scratch,
+                void* out_bf16, int64_t out_row_stride, void* stream);
+
+/* Synchronises the plan's last stream and frees its scratch; unknown handles are ignored.
+ * csrc/graph_projection.cuh:159-163 (release). */
+int ss_plan_release(int64_t handle);
+
+/* out[0..7] = {threads, dynamic smem bytes, registers, local bytes, CTAs/SM, token tile,
+ * smem stages, TMEM columns}.  csrc/graph_projection.cuh:85-89,176 (resources). */
+int ss_plan_resources(int64_t handle, int64_t* out, int n_out);
+
+/* Resources of the GEMM kernel that a problem of this size would use (no plan needed); same
+ * eight values as ss_plan_resources.  csrc/dualscale_sm80.cu:282-291 (configure_t). */
+int ss_gemm_resources(int64_t m, int64_t n, int64_t pk, int64_t* out, int n_out);
+
+/* ---- device status ------------------------------------------------------------------------ */
+
+/* Synchronises `stream` and returns (and clears) the device status word of the current device:
+ * 0 = no kernel gave up on a bounded wait since the last read. */
+int ss_device_status(void* stream, int32_t* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLIDESPARSE_B200_H */

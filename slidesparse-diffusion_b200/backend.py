@@ -1,0 +1,470 @@
+"""Build and load the sm_100a native library; register the reference's torch op names on it.
+
+Host-side mirror of `sdacc/w8a8_slidesparse/backend.py` (build_native :17-70, load_native
+:73-118).  The native artefact is a thin C-ABI shared library (include/slidesparse_b200.h) built
+with nvcc for sm_100a only -- no CUTLASS, no Triton, no second backend, no CPU fallback: every
+operator below raises if the library is missing.
+
+The operators keep the reference's names and schemas (csrc/dualscale_sm80.cu:400-406,
+csrc/projection_sm80.cu:154-169, csrc/graph_projection.cuh:178-195) so callers that look them up
+through `torch.ops.sdacc_*` keep working; `config` arguments are validated and otherwise ignored
+(the SM80 tile identifiers mean nothing here, the library picks its own tile).
+"""
+import ctypes
+import hashlib
+import json
+import os
+import subprocess
+from pathlib import Path
+
+import torch
+
+from .packing import group_size, lifted_k
+
+SS_E_ARG, SS_E_CUDA, SS_E_FORMAT, SS_E_HANDLE, SS_E_DEVICE, SS_E_LIMIT = -1, -2, -3, -4, -5, -6
+LIBRARY_NAME = "libslidesparse_b200.so"
+SOURCES = ("ss_api.cu", "ss_gemm.cu", "ss_frontend.cu", "ss_pack.cu")
+ARCH = "sm_100a"
+VALID_CONFIGS = (0, 1, 2, 3, 4, 5, 6, 11, 12, 13, 14, 15, 16, 17)
+
+_PACKAGE = Path(__file__).resolve().parent
+_lib = None
+_loaded_sha = None
+_ops_registered = False
+
+
+def sha(path):
+    return hashlib.sha256(Path(path).read_bytes()).hexdigest()
+
+
+def default_directory():
+    """Where build_native puts, and library() looks for, the in-tree artefact."""
+    return _PACKAGE / "native_sm100a"
+
+
+def _source_identity():
+    csrc = _PACKAGE / "csrc"
+    files = sorted(p for p in csrc.iterdir() if p.suffix in (".cu", ".cuh"))
+    files.append(_PACKAGE.parent / "include" / "slidesparse_b200.h")
+    return {p.name: sha(p) for p in files}
+
+
+def build_native(output=None, arch=ARCH, force=False):
+    """Offline build, without initialising CUDA; call before measurement.
+
+    Compiles csrc/*.cu into <output>/libslidesparse_b200.so with
+    `nvcc -gencode arch=compute_100a,code=sm_100a` and writes receipt.json (source / library
+    hashes, torch and CUDA versions, the command).  Returns the receipt.  An up-to-date artefact
+    is kept unless force=True.
+    """
+    if torch.cuda.is_initialized():
+        raise RuntimeError("build in a fresh CPU-only process")
+    if arch != ARCH:
+        raise ValueError("this library is written for sm_100a only")
+    output = Path(output) if output is not None else default_directory()
+    output.mkdir(parents=True, exist_ok=True)
+    target, receipt_path = output / LIBRARY_NAME, output / "receipt.json"
+    identity = _source_identity()
+    if not force and target.exists() and receipt_path.exists():
+        old = json.loads(receipt_path.read_text())
+        if old.get("complete") and old.get("source_dependencies") == identity and old.get("library_sha") == sha(target):
+            return old
+    nvcc = str(Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "bin/nvcc")
+    cmd = [nvcc, "-std=c++17", "-O3", "--shared", "-Xcompiler", "-fPIC", "-lineinfo", "-Xptxas=-v",
+           "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd += [str(_PACKAGE / "csrc" / name) for name in SOURCES]
+    cmd += ["-o", str(target)]
+    log = output / "compile.log"
+    with log.open("w") as f:
+        subprocess.run(cmd, check=True, stdout=f, stderr=subprocess.STDOUT)
+    receipt = dict(complete=True, arch=arch, library_sha=sha(target), source_dependencies=identity,
+                   torch=torch.__version__, cuda=torch.version.cuda, command=cmd,
+                   compile_log_sha=sha(log), cuda_initialized=torch.cuda.is_initialized())
+    receipt_path.write_text(json.dumps(receipt, indent=2) + "\n")
+    return receipt
+
+
+def _declare(lib):
+    c = ctypes
+    vp, i64, i32 = c.c_void_p, c.c_int64, c.c_int
+    lib.ss_last_error.restype = c.c_char_p
+    sigs = {
+        "ss_query": [i32, vp, i32],
+        "ss_lifted_k": [i64, i32, vp, vp],
+        "ss_slide_weight_cpu": [vp, i64, i64, i32, vp],
+        "ss_pack_cpu": [vp, i64, i64, i64, vp, vp, vp],
+        "ss_meta_convert": [vp, vp, i64, i64, i32],
+        "ss_weight_grid_device": [vp, i64, i64, vp, vp, vp],
+        "ss_pack_device": [vp, i64, i64, i32, vp, vp, vp, vp],
+        "ss_quantize_lift": [vp, i64, i64, i64, i32, vp, vp, vp],
+        "ss_gemm_run": [vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, i64, vp],
+        "ss_gemm_int32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp],
+        "ss_projection": [vp, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, vp],
+        "ss_plan_create": [vp, vp, vp, vp, i64, i64, i64, i64, i32, vp],
+        "ss_plan_run": [i64, vp, i64, vp, vp, vp, i64, vp],
+        "ss_plan_release": [i64],
+        "ss_plan_resources": [i64, vp, i32],
+        "ss_gemm_resources": [i64, i64, i64, vp, i32],
+        "ss_device_status": [vp, vp],
+    }
+    for name, args in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = args, i32
+    return lib
+
+
+def load_native(directory=None):
+    """Load once (never touching CUDA) and register the operators.  Returns the receipt.
+
+    Refuses a binary whose receipt does not match the sources next to this file, and refuses a
+    second, different binary in the same process.
+    """
+    global _lib, _loaded_sha
+    directory = Path(directory) if directory is not None else default_directory()
+    receipt_path, target = directory / "receipt.json", directory / LIBRARY_NAME
+    if not receipt_path.exists() or not target.exists():
+        raise FileNotFoundError(f"no native library in {directory}: run build_native() first")
+    receipt = json.loads(receipt_path.read_text())
+    if not receipt.get("complete") or receipt.get("arch") != ARCH:
+        raise ValueError("native receipt is incomplete or for another architecture")
+    if receipt.get("source_dependencies") != _source_identity():
+        raise ValueError("native source dependency identity differs; rebuild this release")
+    if receipt.get("library_sha") != sha(target):
+        raise ValueError("native binary differs from its receipt")
+    if _lib is not None:
+        if _loaded_sha != receipt["library_sha"]:
+            raise RuntimeError("a different native binary is already loaded in this process")
+        return receipt
+    _lib = _declare(ctypes.CDLL(str(target)))
+    _loaded_sha = receipt["library_sha"]
+    _register_ops()
+    return receipt
+
+
+def library():
+    """The loaded C-ABI library; loads the in-tree build on first use, raises if there is none."""
+    if _lib is None:
+        try:
+            load_native()
+        except (FileNotFoundError, ValueError) as e:
+            raise RuntimeError(
+                "the sm_100a native library is not built/loaded (no fallback exists): " + str(e)) from e
+    return _lib
+
+
+def check(rc):
+    if rc == 0:
+        return
+    message = library().ss_last_error().decode(errors="replace")
+    if rc in (SS_E_ARG, SS_E_FORMAT, SS_E_LIMIT):
+        raise ValueError(message)
+    raise RuntimeError(message)
+
+
+# ------------------------------------------------------------------------------------------
+# thin typed wrappers (device pointers in, nothing allocated behind the caller's back)
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else None
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _check_config(config):
+    if config not in VALID_CONFIGS:
+        raise ValueError("invalid config")
+
+
+def pack_weight(lifted, padded_k, layout="b200"):
+    """CPU int8 [n,kl] -> (packed int8 [pn,pk/2], metadata int32 [pn*pk/32])."""
+    if lifted.device.type != "cpu" or lifted.dtype != torch.int8 or lifted.ndim != 2 or not lifted.is_contiguous():
+        raise ValueError("pack needs contiguous CPU int8 weight")
+    n, kl = lifted.shape
+    pk = int(padded_k)
+    if not (n > 0 and kl > 0 and pk >= kl and pk % 128 == 0):
+        raise ValueError("invalid128-K padding")
+    pn = -(-n // 32) * 32
+    packed = torch.empty((pn, pk // 2), dtype=torch.int8)
+    metadata = torch.empty(pn * pk // 32, dtype=torch.int32)
+    raw, hw = (_ptr(metadata), None) if layout == "raw" else (None, _ptr(metadata))
+    check(library().ss_pack_cpu(_ptr(lifted), n, kl, pk, _ptr(packed), raw, hw))
+    return packed, metadata
+
+
+def convert_metadata(metadata, pn, pk, to_b200=True):
+    src = metadata.detach().cpu().contiguous().view(torch.int32)
+    dst = torch.empty_like(src)
+    check(library().ss_meta_convert(_ptr(src), _ptr(dst), pn, pk, 1 if to_b200 else 0))
+    return dst
+
+
+def quantize_lift_into(flat, group, q, sa):
+    m, k = flat.shape
+    with torch.cuda.device(flat.device):
+        check(library().ss_quantize_lift(_ptr(flat), flat.stride(0), m, k, group, _ptr(q), _ptr(sa),
+                                         _stream(flat.device)))
+
+
+def _flatten_input(x, k):
+    flat = x.reshape(-1, k)
+    if flat.stride(-1) != 1:
+        flat = flat.contiguous()
+    return flat
+
+
+def _quantize(input, group):
+    if not input.is_cuda or input.dtype != torch.bfloat16 or input.ndim < 1:
+        raise ValueError("BF16 CUDA input required")
+    group = group_size(int(group))
+    k = input.shape[-1]
+    flat = _flatten_input(input, k)
+    m = flat.shape[0]
+    if m <= 0:
+        raise ValueError("empty input unsupported by native frontend")
+    _, pk = lifted_k(k, group)
+    pm = -(-m // 32) * 32
+    q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
+    sa = torch.empty(pm, dtype=torch.float32, device=input.device)
+    quantize_lift_into(flat, group, q, sa)
+    return q, sa
+
+
+def _check_weights(q_device, packed, metadata, sw, bias, pk):
+    for t in (packed, metadata, sw, bias):
+        if t.device != q_device or not t.is_contiguous():
+            raise ValueError("buffer device/layout mismatch")
+    if packed.dtype != torch.int8 or packed.ndim != 2 or metadata.dtype != torch.int32:
+        raise ValueError("packed types")
+    if sw.dtype != torch.float32 or bias.dtype != torch.float32:
+        raise ValueError("scale/bias must be FP32")
+    if packed.shape[0] % 32 or packed.shape[1] * 2 != pk:
+        raise ValueError("padding mismatch")
+    if metadata.numel() != packed.shape[0] * pk // 32:
+        raise ValueError("metadata/token scales size")
+
+
+def _check_addend(addend, device, m, n):
+    if addend is None:
+        return None
+    if (not addend.is_cuda or addend.device != device or addend.dtype != torch.bfloat16 or addend.ndim != 2
+            or addend.shape != (m, n) or addend.stride(1) != 1):
+        raise ValueError("addend must be BF16 [M,N] with unit column stride")
+    return addend
+
+
+def _run(q, packed, metadata, sa, sw, bias, m, n, config, output_addend=None):
+    if not q.is_cuda or q.dtype != torch.int8 or q.ndim != 2 or not q.is_contiguous():
+        raise ValueError("q must be row-major CUDA int8")
+    pm, pk = q.shape
+    if pk % 128 or pm % 32:
+        raise ValueError("padding mismatch")
+    _check_weights(q.device, packed, metadata, sw, bias, pk)
+    if sa.dtype != torch.float32 or sa.numel() != pm or sa.device != q.device:
+        raise ValueError("metadata/token scales size")
+    pn = packed.shape[0]
+    if not (0 < m <= pm and 0 < n <= pn and sw.numel() >= n and (bias.numel() == 0 or bias.numel() >= n)):
+        raise ValueError("original dimensions/channels")
+    _check_config(config)
+    addend = _check_addend(output_addend, q.device, m, n)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=q.device)
+    with torch.cuda.device(q.device):
+        check(library().ss_gemm_run(_ptr(q), _ptr(packed), _ptr(metadata), _ptr(sa), _ptr(sw), _ptr(bias),
+                                    _ptr(addend), addend.stride(0) if addend is not None else 0,
+                                    _ptr(out), n, m, n, pm, pn, pk, _stream(q.device)))
+    return out
+
+
+def gemm_int32(q, packed, metadata, m, n):
+    """Raw INT32 accumulators [m,n] of the sparse contraction (debug / parity epilogue)."""
+    pm, pk = q.shape
+    out = torch.empty((m, n), dtype=torch.int32, device=q.device)
+    with torch.cuda.device(q.device):
+        check(library().ss_gemm_int32(_ptr(q), _ptr(packed), _ptr(metadata), _ptr(out), m, n, pm,
+                                      packed.shape[0], pk, _stream(q.device)))
+    return out
+
+
+def _projection(input, packed, metadata, scales, bias, group, n, config, output_addend=None):
+    if not input.is_cuda or input.dtype != torch.bfloat16 or input.ndim < 1:
+        raise ValueError("BF16 CUDA input required")
+    group = group_size(int(group))
+    _check_config(config)
+    k = input.shape[-1]
+    flat = _flatten_input(input, k)
+    m = flat.shape[0]
+    if m <= 0:
+        raise ValueError("empty input unsupported by native frontend")
+    _, pk = lifted_k(k, group)
+    pm = -(-m // 32) * 32
+    _check_weights(input.device, packed, metadata, scales, bias, pk)
+    pn = packed.shape[0]
+    if not (0 < n <= pn and scales.numel() >= n and (bias.numel() == 0 or bias.numel() >= n)):
+        raise ValueError("original dimensions/channels")
+    addend = output_addend
+    if addend is not None:
+        addend = _check_addend(addend.reshape(-1, n), input.device, m, n)
+    q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
+    sa = torch.empty(pm, dtype=torch.float32, device=input.device)
+    out = torch.empty((*input.shape[:-1], n), dtype=torch.bfloat16, device=input.device)
+    with torch.cuda.device(input.device):
+        check(library().ss_projection(_ptr(flat), flat.stride(0), m, k, group, _ptr(packed), _ptr(metadata),
+                                      _ptr(scales), _ptr(bias), _ptr(addend),
+                                      addend.stride(0) if addend is not None else 0, n, pn,
+                                      _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
+    return out
+
+
+def _configure(anchor, config, has_addend=False):
+    if not anchor.is_cuda:
+        raise ValueError("CUDA anchor required")
+    _check_config(config)
+    info = (ctypes.c_int64 * 8)()
+    with torch.cuda.device(anchor.device):
+        check(library().ss_query(anchor.device.index, info, 8))
+        if info[2] != 10:
+            raise RuntimeError("this library is built for sm_100a (B200) only")
+        pn, half = anchor.shape
+        res = (ctypes.c_int64 * 8)()
+        check(library().ss_gemm_resources(4096, pn, 2 * half, res, 8))
+    base = [int(v) for v in res[:5]]
+    return base + base
+
+
+_plan_devices = {}
+
+
+def _prepare(packed, metadata, scales, bias, k, m, n, group, config, packed16):
+    if not packed.is_cuda or m <= 0 or n <= 0:
+        raise ValueError("prepared graph geometry")
+    group = group_size(int(group))
+    _check_config(config)
+    _, pk = lifted_k(k, group)
+    _check_weights(packed.device, packed, metadata, scales, bias, pk)
+    pn = packed.shape[0]
+    if not (pn >= n and scales.numel() >= n and (bias.numel() == 0 or bias.numel() >= n)):
+        raise ValueError("prepared packing")
+    handle = ctypes.c_int64(0)
+    with torch.cuda.device(packed.device):
+        check(library().ss_plan_create(_ptr(packed), _ptr(metadata), _ptr(scales), _ptr(bias), k, m, n, pn,
+                                       group, ctypes.byref(handle)))
+    _plan_devices[handle.value] = (packed.device, m, k, n, pk)
+    return handle.value
+
+
+def _prepared_run(input, handle, n):
+    if handle not in _plan_devices:
+        raise RuntimeError("prepared graph handle absent")
+    device, m, k, plan_n, pk = _plan_devices[handle]
+    if (not input.is_cuda or input.device != device or input.dtype != torch.bfloat16
+            or input.shape[-1] != k):
+        raise ValueError("prepared input identity")
+    if input.numel() != m * k or n != plan_n:
+        raise ValueError("prepared shape changed")
+    flat = _flatten_input(input, k)
+    out = torch.empty((*input.shape[:-1], n), dtype=torch.bfloat16, device=device)
+    stream = torch.cuda.current_stream(device)
+    q = sa = None
+    lib = library()
+    with torch.cuda.device(device):
+        rc = lib.ss_plan_run(handle, _ptr(flat), flat.stride(0), None, None, _ptr(out), n,
+                             ctypes.c_void_p(stream.cuda_stream))
+        if rc == SS_E_ARG and b"caller scratch" in lib.ss_last_error():
+            # another stream, or an outer graph capture: independent scratch from torch's allocator
+            pm = -(-m // 32) * 32
+            q = torch.empty((pm, pk), dtype=torch.int8, device=device)
+            sa = torch.empty(pm, dtype=torch.float32, device=device)
+            rc = lib.ss_plan_run(handle, _ptr(flat), flat.stride(0), _ptr(q), _ptr(sa), _ptr(out), n,
+                                 ctypes.c_void_p(stream.cuda_stream))
+        check(rc)
+    return out
+
+
+def _release(handle):
+    _plan_devices.pop(handle, None)
+    check(library().ss_plan_release(handle))
+
+
+def _resources(handle):
+    res = (ctypes.c_int64 * 8)()
+    device = _plan_devices[handle][0]
+    with torch.cuda.device(device):
+        check(library().ss_plan_resources(handle, res, 8))
+    return [int(v) for v in res[:5]]
+
+
+def device_status(device=None):
+    """Synchronise the current stream and return (and clear) the device's kernel status word."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    status = ctypes.c_int32(0)
+    with torch.cuda.device(device):
+        check(library().ss_device_status(_stream(device), ctypes.byref(status)))
+    return status.value
+
+
+# ------------------------------------------------------------------------------------------
+# torch operator registration under the reference's names
+
+_libraries = []
+
+
+def _register_ops():
+    global _ops_registered
+    if _ops_registered:
+        return
+    _ops_registered = True
+    Library = torch.library.Library
+
+    dual = Library("sdacc_dualscale_sm80", "DEF")
+    dual.define("pack_cpu(Tensor weight,int padded_k)->(Tensor,Tensor)")
+    dual.define("configure(Tensor anchor,int config,bool has_addend=False)->int[]")
+    dual.define("run(Tensor q,Tensor packed,Tensor metadata,Tensor sa,Tensor sw,Tensor bias,int m,int n,"
+                "int config,Tensor? output_addend=None)->Tensor")
+    dual.impl("pack_cpu", lambda weight, padded_k: pack_weight(weight, padded_k), "CPU")
+    dual.impl("configure", _configure, "CUDA")
+    dual.impl("run", _run, "CUDA")
+
+    mild = Library("sdacc_mild_projection_sm80", "DEF")
+    proj = ("(Tensor input,Tensor packed,Tensor metadata,Tensor scales,Tensor bias,int group,int n,int config,"
+            "Tensor? output_addend=None)->Tensor")
+    mild.define("quantize_packed16(Tensor input,int group)->(Tensor,Tensor)")
+    mild.define("projection_packed16" + proj)
+    mild.define("quantize(Tensor input,int group)->(Tensor,Tensor)")
+    mild.define("quantize_scalar(Tensor input)->(Tensor,Tensor)")
+    mild.define("projection" + proj)
+    mild.define("projection_scalar" + proj)
+    # One front-end serves all three reference variants: they produce identical bits.
+    mild.impl("quantize", _quantize, "CUDA")
+    mild.impl("quantize_packed16", _quantize, "CUDA")
+    mild.impl("quantize_scalar", lambda input: _quantize(input, 4), "CUDA")
+    for name in ("projection", "projection_packed16", "projection_scalar"):
+        mild.impl(name, _projection, "CUDA")
+
+    prepared = Library("sdacc_prepared_projection_sm80", "DEF")
+    prep = ("(Tensor packed,Tensor metadata,Tensor scales,Tensor bias,int k,int m,int n,int group,int config,"
+            "bool packed16)->int")
+    for name in ("prepare_direct2", "prepare_singlepatch", "prepare"):
+        prepared.define(name + prep)
+        prepared.impl(name, _prepare, "CUDA")
+    prepared.define("resources(int handle)->int[]")
+    prepared.define("run(Tensor input,int handle,int n)->Tensor")
+    prepared.define("release(int handle)->()")
+    prepared.impl("run", _prepared_run, "CUDA")
+    prepared.impl("release", _release, "CompositeExplicitAutograd")
+    prepared.impl("resources", _resources, "CompositeExplicitAutograd")
+    _libraries.extend([dual, mild, prepared])
+
+    @torch.library.register_fake("sdacc_dualscale_sm80::run")
+    def _fake_run(q, packed, metadata, sa, sw, bias, m, n, config, output_addend=None):
+        return q.new_empty((m, n), dtype=torch.bfloat16)
+
+    def _fake_projection(x, packed, metadata, scales, bias, group, n, config, output_addend=None):
+        return x.new_empty((*x.shape[:-1], n))
+
+    for name in ("projection", "projection_scalar", "projection_packed16"):
+        torch.library.register_fake("sdacc_mild_projection_sm80::" + name)(_fake_projection)
+
+    @torch.library.register_fake("sdacc_prepared_projection_sm80::run")
+    def _fake_prepared(x, handle, n):
+        return x.new_empty((*x.shape[:-1], n))
