@@ -1,0 +1,377 @@
+"""Benchmark of the sparse W8A8 projection path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload ("flux_sweep"): the sliding-sparse projection sweep of the FLUX shapes -- modes 4:6 and
+6:8; (K,N) in {(3072,9216) fused QKV, (3072,12288) MLP fc1, (12288,3072) MLP fc2};
+M in {256, 1024, 1536, 4096, 16384}: 30 complete projections (front-end + GEMM) per step.
+Inputs are seeded synthetic tensors (BF16 N(0,1) activations with 1% outlier channels x20;
+N(0,0.02) weights magnitude-pruned per mode, per-channel INT8).
+
+Printed JSON line (rank 0):
+  value    logical TOPS = sum(2*M*N*K) / device time, inputs resident in HBM, the 30 projections of
+           a step replayed as one CUDA graph (host launch cost would otherwise hide the kernels)
+  e2e      the same metric through PackedLinear.forward with HOST buffers: every step copies all
+           activations from pinned host memory to the device and all outputs back
+  roofline the GEMM kernel alone (CUDA events around GEMM-only launches), against the 2:4-sparse
+           INT8 tensor peak derived from the measured dense BF16 peak (x4)
+  cpu_baseline  the oracle port of the reference path timed on the host cores (bounded sample)
+
+`--impl reference` times the reference's CPU implementation of the path (its quantise / slide /
+pack restated in oracle/, with an int32 torch matmul) on a bounded sample of the same workload.
+With N > 1 (torchrun) every rank runs the sweep on its own weight shard (independent output
+channel shards, no collective); value = all ranks' operations / max-over-ranks time.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODES = (6, 8)
+SHAPES = ((3072, 9216), (3072, 12288), (12288, 3072))      # (K, N)
+TOKENS = (256, 1024, 1536, 4096, 16384)
+SAMPLE_TOKENS = 48            # rows per projection in the CPU sample (M = 1536 case)
+
+
+def logical_ops(tokens=TOKENS):
+    return sum(2 * m * n * k for _ in MODES for (k, n) in SHAPES for m in tokens)
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return dict(hbm_gbs=data["hbm_gbs"], bf16_tflops=data["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+def cpu_prepare(oracle, oracle_c):
+    """Offline part of the CPU sample (weights pruned, quantised, slid; activations drawn)."""
+    import torch
+    prepared = []
+    for mode in MODES:
+        for (k, n) in SHAPES:
+            qweight, scales = oracle.make_weight(n, k, mode, seed=mode * 100 + n % 97)
+            lifted = oracle_c.slide_weight(qweight, mode)
+            x = oracle.make_activation(SAMPLE_TOKENS, k, seed=k)
+            prepared.append((mode, k, n, torch.from_numpy(lifted).to(torch.int32).T.contiguous(), scales, x))
+    return prepared
+
+
+def cpu_sample(oracle, prepared, threads):
+    """One pass of the reference path on the host: the six (mode, shape) projections at the
+    M=1536 configuration restricted to its first SAMPLE_TOKENS token rows.  Returns ops, seconds."""
+    import torch
+    torch.set_num_threads(threads)
+    ops = sum(2 * SAMPLE_TOKENS * n * k for (_, k, n, _, _, _) in prepared)
+    start = time.perf_counter()
+    for mode, k, n, lifted_t, scales, x in prepared:
+        q, sa = oracle.quantize_lift(x, mode)
+        acc = (torch.from_numpy(q[:SAMPLE_TOKENS, :lifted_t.shape[0]]).to(torch.int32) @ lifted_t).numpy()
+        oracle.epilogue(acc, sa, scales, None)
+    return ops, time.perf_counter() - start
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    from __graft_entry__ import load_oracle
+    oracle, oracle_c = load_oracle()
+    threads = os.cpu_count() or 1
+    prepared = cpu_prepare(oracle, oracle_c)
+    for _ in range(args.warmup):
+        cpu_sample(oracle, prepared, threads)
+    total_ops, total_s = 0, 0.0
+    for _ in range(args.steps):
+        ops, seconds = cpu_sample(oracle, prepared, threads)
+        total_ops += ops
+        total_s += seconds
+    value = total_ops / total_s / 1e12
+    sample = (f"modes 4:6+6:8 x 3 FLUX shapes at M=1536 restricted to the first {SAMPLE_TOKENS} token rows "
+              f"({total_ops / args.steps / 1e9:.1f} GOP per step); quantise+lift, int32 torch matmul, epilogue")
+    print(json.dumps({
+        "impl": "reference", "metric": "sparse_w8a8_linear_tops", "value": value, "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total_s / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "flux_sweep", "modes": ["4:6", "6:8"], "shapes_kn": SHAPES, "tokens": TOKENS},
+        "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="native", choices=("native", "reference"))
+    parser.add_argument("--tokens", type=str, default=None, help="comma-separated M values (debug)")
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package, load_oracle
+    sdk = load_package()
+    sdk.load_native()
+    oracle, oracle_c = load_oracle()
+    tokens = tuple(int(t) for t in args.tokens.split(",")) if args.tokens else TOKENS
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    # ---- build the workload (seeded; each rank owns a different weight shard) ----------------
+    ops = {}
+    for mode in MODES:
+        for (k, n) in SHAPES:
+            qweight, scales = oracle.make_weight(n, k, mode, seed=mode * 100 + n % 97 + 1000 * rank)
+            bias = (0.1 * torch.randn(n, generator=torch.Generator().manual_seed(n + rank))).float()
+            ops[(mode, k, n)] = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales),
+                                                         bias, mode).to(device)
+    host_x = {}
+    for k in sorted({k for k, _ in SHAPES}):
+        big = oracle.make_activation(max(tokens), k, seed=k)
+        for m in tokens:
+            host_x[(m, k)] = big[:m].contiguous().pin_memory()
+    dev_x = {key: value.to(device) for key, value in host_x.items()}
+    calls = [(mode, k, n, m) for mode in MODES for (k, n) in SHAPES for m in tokens]
+    step_ops = sum(2 * m * n * k for (_, k, n, m) in calls)
+
+    def step():
+        return [ops[(mode, k, n)](dev_x[(m, k)]) for (mode, k, n, m) in calls]
+
+    # correctness spot check before timing: smallest projection against the oracle
+    mode, k, n, m = min(calls, key=lambda c: c[3] * c[2] * c[1])
+    check_rows = min(m, 64)
+    y = ops[(mode, k, n)](dev_x[(m, k)][:check_rows])
+    qweight, scales = oracle.make_weight(n, k, mode, seed=mode * 100 + n % 97 + 1000 * rank)
+    bias = (0.1 * torch.randn(n, generator=torch.Generator().manual_seed(n + rank))).float().numpy()
+    expect = oracle.projection(host_x[(m, k)][:check_rows], qweight, scales, bias, mode)["out_bits"]
+    got = y.view(torch.int16).cpu().numpy().view(np.uint16)
+    if not np.array_equal(got, expect):
+        raise SystemExit("bench: projection output differs from the oracle")
+
+    # ---- value: CUDA-graph replay of one step, inputs resident ------------------------------------
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outputs = step()
+    for _ in range(args.warmup):
+        graph.replay()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        begin.record()
+        for _ in range(args.steps):
+            graph.replay()
+        end.record()
+        barrier()
+    elapsed_ms = begin.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    value = world * step_ops * args.steps / (elapsed_ms * 1e-3) / 1e12
+    import slidesparse_diffusion_b200.backend as backend
+    if backend.device_status(device) != 0:
+        raise SystemExit("bench: a kernel reported a bounded wait that ran out")
+
+    # ---- roofline legs: GEMM alone and front-end alone, CUDA events on the launching stream ---
+    pk_of = {(mode, k): sdk.lifted_k(k, mode)[1] for mode in MODES for (k, _) in SHAPES}
+    quantised = {(mode, m, k): sdk.quantize_lift(dev_x[(m, k)], mode)
+                 for mode in MODES for k in sorted({k for k, _ in SHAPES}) for m in tokens}
+
+    def gemm_only():
+        for (mode, k, n, m) in calls:
+            op = ops[(mode, k, n)]
+            q, sa = quantised[(mode, m, k)]
+            torch.ops.sdacc_dualscale_sm80.run(q, op.packed, op.metadata, sa, op.scales, op.bias, m, n, 5, None)
+
+    def frontend_only():
+        for (mode, m, k) in quantised:
+            torch.ops.sdacc_mild_projection_sm80.quantize(dev_x[(m, k)], mode)
+
+    def timed_graph(fn, repeats):
+        s = torch.cuda.Stream(device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            fn()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b.record()
+        for _ in range(repeats):
+            g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        return b.elapsed_time(e) / repeats
+
+    gemm_ms = timed_graph(gemm_only, max(3, args.steps // 2))
+    front_ms = timed_graph(frontend_only, max(3, args.steps // 2))
+    pk = peaks()
+    sparse_peak = 4.0 * pk["bf16_tflops"]
+    gemm_tops = step_ops / (gemm_ms * 1e-3) / 1e12
+    front_bytes = sum(2 * m * k + (-(-m // 32) * 32) * (pk_of[(mode, k)] + 4) for (mode, m, k) in quantised)
+    front_gbs = front_bytes / (front_ms * 1e-3) / 1e9
+
+    # ---- e2e: host buffers through the public module ---------------------------------------------
+    host_out = {c: torch.empty((c[3], c[2]), dtype=torch.bfloat16).pin_memory() for c in calls}
+    h2d = sum(t.numel() * 2 for t in host_x.values())
+    d2h = sum(t.numel() * 2 for t in host_out.values())
+
+    def e2e_step():
+        staged = {key: value.to(device, non_blocking=True) for key, value in host_x.items()}
+        for c in calls:
+            mode, k, n, m = c
+            host_out[c].copy_(ops[(mode, k, n)](staged[(m, k)]), non_blocking=True)
+
+    e2e_steps = max(3, args.steps // 4)
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    begin.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    end.record()
+    barrier()
+    e2e_ms = begin.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * step_ops * e2e_steps / (e2e_ms * 1e-3) / 1e12
+
+    # ---- CPU baseline (rank 0, single GPU runs only) ----------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        prepared = cpu_prepare(oracle, oracle_c)
+        cpu_sample(oracle, prepared, threads)
+        total_ops, total_s = 0, 0.0
+        while total_s < 10.0:
+            o, s = cpu_sample(oracle, prepared, threads)
+            total_ops += o
+            total_s += s
+        cpu = {"value": total_ops / total_s / 1e12, "unit": "TOPS", "cores": threads, "kind": "port",
+               "sample": f"6 projections (4:6+6:8 x 3 FLUX shapes) at M=1536 restricted to {SAMPLE_TOKENS} "
+                         f"token rows, repeated for {total_s:.1f} s"}
+
+    if rank == 0:
+        line = {
+            "metric": "sparse_w8a8_linear_tops", "value": value, "unit": "TOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+            "data": "synthetic",
+            "config": {"workload": "flux_sweep", "modes": ["4:6", "6:8"], "shapes_kn": SHAPES,
+                       "tokens": tokens, "projections_per_step": len(calls),
+                       "l2": "inputs+outputs per step (3.0 GB) exceed L2", "parallelism": f"column-shards x{world}",
+                       "pct_of_nominal_sparse_int8_peak_9000": 100 * value / world / 9000.0,
+                       "pct_of_nominal_dense_int8_peak_4500": 100 * value / world / 4500.0},
+            "clocks": clocks.summary(),
+            "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": 2 * len(calls) * args.steps,
+            "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": sparse_peak, "unit": "TFLOP/s",
+                         "frac": gemm_tops / sparse_peak, "traffic": None,
+                         "kernel": "sparse_gemm_kernel (30 launches per step)",
+                         "peak_source": f"4 x {pk['source']} dense bf16 {pk['bf16_tflops']} TFLOP/s "
+                                        "(2:4-sparse INT8 proxy; nominal 9000)"},
+            "roofline_frontend": {"bound": "hbm", "achieved": front_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                  "frac": front_gbs / pk["hbm_gbs"], "kernel": "quant_lift_kernel"},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

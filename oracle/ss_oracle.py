@@ -226,11 +226,16 @@ def epilogue(acc, sa, sw, bias=None, addend=None):
     return round_bf16(y)
 
 
+def channel_scales(weight):
+    """scale = 2*rowabsmax/255, 1 for an all-zero row (reconstruction.py:41-49)."""
+    mx = np.abs(np.asarray(weight, dtype=np.float32)).max(axis=1)
+    return np.where(mx > 0, (np.float32(2.0) * mx / np.float32(255.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+
+
 def weight_grid(weight):
     """fp32 [n,k] -> (int8 [n,k], fp32 scales [n]): scale = 2*rowabsmax/255 (1 if zero)."""
     w = np.asarray(weight, dtype=np.float32)
-    mx = np.abs(w).max(axis=1)
-    scales = np.where(mx > 0, (np.float32(2.0) * mx / np.float32(255.0)).astype(np.float32), np.float32(1.0)).astype(np.float32)
+    scales = channel_scales(w)
     q = np.clip(np.rint((w / scales[:, None]).astype(np.float32)), -128, 127).astype(np.int8)
     return q, scales
 
@@ -244,9 +249,11 @@ def magnitude_prune(weight, mode):
     l = group_size(mode)
     pad = (-k) % l
     g = np.pad(np.abs(w), ((0, 0), (0, pad)), constant_values=-1.0).reshape(n, -1, l)
-    order = np.argsort(g, axis=-1, kind="stable")[..., :2]
     mask = np.zeros(g.shape, dtype=bool)
-    np.put_along_axis(mask, order, True, axis=-1)
+    for _ in range(2):                      # argmin returns the lowest index among ties
+        first = np.argmin(g, axis=-1)[..., None]
+        np.put_along_axis(mask, first, True, axis=-1)
+        np.put_along_axis(g, first, np.float32(np.inf), axis=-1)
     mask = mask.reshape(n, -1)[:, :k]
     w[mask] = 0
     return w, mask
@@ -257,7 +264,7 @@ def make_weight(n, k, mode, seed=0, std=0.02):
     Returns (qweight int8 [n,k], scales fp32 [n])."""
     gen = torch.Generator().manual_seed(seed)
     w = (torch.randn(n, k, generator=gen) * std).to(torch.bfloat16).float().numpy()
-    _, scales = weight_grid(w)
+    scales = channel_scales(w)
     pruned, mask = magnitude_prune(w, mode)
     q = np.clip(np.rint((pruned / scales[:, None]).astype(np.float32)), -128, 127).astype(np.int8)
     q[mask] = 0

@@ -1,0 +1,140 @@
+"""Parity of the CUDA path with the CPU oracle, called through the C ABI.  Bit-exact for the
+INT8 activations, scales, packed weights, metadata and INT32 accumulators; the BF16 output is
+compared bit-for-bit as well (the stated tolerance is 1 BF16 ulp = relative 2^-8; mismatches are
+counted and must be zero, the ulp bound is asserted as a backstop)."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import bits, c_gemm_int32, c_gemm_run, c_quantize_lift, prepare_case, ptr, stream, check
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return (t if dtype is None else t.view(dtype)).to(DEV)
+
+
+@pytest.mark.parametrize("mode", [4, 6, 8])
+@pytest.mark.parametrize("m,k", [(1, 8), (31, 40), (32, 128), (33, 130), (200, 1152), (64, 2432),
+                                 (96, 3072), (40, 12288), (7, 4100), (5, 16384)])
+def test_frontend_bit_exact(backend, oracle, mode, m, k):
+    x = oracle.make_activation(m, k, seed=m * 31 + k)
+    q_ref, sa_ref = oracle.quantize_lift(x, mode)
+    q, sa = c_quantize_lift(backend, x.to(DEV), mode)
+    torch.cuda.synchronize()
+    assert np.array_equal(sa.cpu().numpy(), sa_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+@pytest.mark.parametrize("mode", [4, 6, 8])
+def test_frontend_strided_and_unaligned_rows(backend, oracle, mode):
+    wide = oracle.make_activation(50, 15360 // 8 + 6, seed=5).to(DEV)
+    for lo, hi in ((384, 384 + 1536), (3, 3 + 1001), (0, 77)):
+        view = wide[:, lo:hi]
+        q_ref, sa_ref = oracle.quantize_lift(view.cpu().contiguous(), mode)
+        q, sa = c_quantize_lift(backend, view, mode)
+        assert np.array_equal(q.cpu().numpy(), q_ref) and np.array_equal(sa.cpu().numpy(), sa_ref)
+
+
+def test_frontend_nonfinite(backend, oracle):
+    x = oracle.make_activation(4, 256, seed=1)
+    x[0, 3] = float("nan")
+    x[1, 7] = float("inf")
+    x[2, :] = 0
+    x[3, 100] = float("-inf")
+    for mode in (4, 6, 8):
+        q_ref, sa_ref = oracle.quantize_lift(x, mode)
+        q, sa = c_quantize_lift(backend, x.to(DEV), mode)
+        assert np.array_equal(q.cpu().numpy(), q_ref)
+        assert np.array_equal(sa.cpu().numpy(), sa_ref)
+
+
+SHAPES = [(4, 32, 128, 32), (4, 100, 256, 200), (6, 64, 132, 96), (8, 130, 200, 129), (4, 256, 1152, 512),
+          (6, 300, 1152, 384), (8, 257, 1152, 640), (6, 128, 2432, 256), (4, 512, 4608, 1152),
+          (8, 192, 3072, 1024), (4, 1, 64, 1), (6, 40, 38, 30)]
+
+
+@pytest.mark.parametrize("mode,m,k,n", SHAPES)
+def test_gemm_int32_accumulators_bit_exact(backend, oracle, mode, m, k, n):
+    case = prepare_case(oracle, m, k, n, mode, seed=n)
+    q, packed, meta = dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32)
+    acc = c_gemm_int32(backend, q, packed, meta, m, n)
+    torch.cuda.synchronize()
+    assert backend.device_status() == 0
+    assert np.array_equal(acc.cpu().numpy(), case["acc"])
+
+
+@pytest.mark.parametrize("tile", ["64", "128", "192", "256"])
+def test_every_token_tile_is_exact(backend, oracle, monkeypatch, tile):
+    monkeypatch.setenv("SS_TOKEN_TILE", tile)
+    case = prepare_case(oracle, 700, 640, 300, 6, seed=int(tile))
+    q, packed, meta = dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32)
+    acc = c_gemm_int32(backend, q, packed, meta, 700, 300)
+    assert np.array_equal(acc.cpu().numpy(), case["acc"])
+    assert backend.device_status() == 0
+
+
+@pytest.mark.parametrize("mode,m,k,n", SHAPES)
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_gemm_bf16_output(backend, oracle, oracle_c, mode, m, k, n, with_bias):
+    case = prepare_case(oracle, m, k, n, mode, seed=n + 1, with_bias=with_bias)
+    q, packed, meta = dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32)
+    sa, sw = dev(case["sa"]), dev(case["scales"])
+    bias = dev(case["bias"]) if with_bias else None
+    out = c_gemm_run(backend, q, packed, meta, sa, sw, bias, m, n)
+    got = bits(out)
+    expect = oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"])
+    assert np.array_equal(expect, case["out_bits"])        # both oracle restatements agree
+    assert int((got != expect).sum()) == 0
+    ref = torch.from_numpy(expect.view(np.int16)).view(torch.bfloat16).float()
+    assert torch.all((out.cpu().float() - ref).abs() <= ref.abs() * 2.0 ** -8)
+
+
+def test_gemm_addend(backend, oracle, oracle_c):
+    m, k, n, mode = 150, 512, 200, 8
+    case = prepare_case(oracle, m, k, n, mode, seed=3)
+    wide = (torch.randn(m, n + 24, generator=torch.Generator().manual_seed(9))).to(torch.bfloat16)
+    addend = wide[:, 8:8 + n]                      # row stride != n
+    out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
+                     dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), m, n,
+                     addend=wide.to(DEV)[:, 8:8 + n])
+    expect = oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"], bits(addend))
+    assert np.array_equal(bits(out), expect)
+
+
+@pytest.mark.parametrize("mode,n,k", [(4, 40, 128), (6, 96, 300), (8, 70, 200), (6, 33, 1153), (8, 64, 2432)])
+def test_device_packer_bit_exact(backend, oracle, mode, n, k):
+    qweight, _ = oracle.make_weight(n, k, mode, seed=k)
+    _, pk = oracle.lifted_k(k, mode)
+    packed_ref, raw = oracle.pack(oracle.slide_weight(qweight, mode), pk)
+    pn = packed_ref.shape[0]
+    packed = torch.full((pn, pk // 2), 0x33, dtype=torch.int8, device=DEV)
+    meta = torch.zeros(pn * pk // 32, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    check(backend, backend.library().ss_pack_device(ptr(dev(qweight)), n, k, mode, ptr(packed), ptr(meta),
+                                                    ptr(status), stream()))
+    assert int(status.item()) == 0
+    assert np.array_equal(packed.cpu().numpy(), packed_ref)
+    assert np.array_equal(meta.cpu().numpy().view(np.uint32), oracle.meta_to_b200(raw, pk))
+
+
+def test_device_packer_flags_bad_structure(backend):
+    qweight = torch.tensor([[1, 2, 3, 4, 5, 0] * 4], dtype=torch.int8, device=DEV)
+    packed = torch.zeros((32, 128), dtype=torch.int8, device=DEV)
+    meta = torch.zeros(32 * 8, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    check(backend, backend.library().ss_pack_device(ptr(qweight), 1, 24, 6, ptr(packed), ptr(meta), ptr(status), stream()))
+    assert int(status.item()) == 1
+
+
+def test_device_weight_grid(backend, oracle):
+    w = (torch.randn(37, 301, generator=torch.Generator().manual_seed(4)) * 0.02)
+    w[5] = 0
+    q_ref, s_ref = oracle.weight_grid(w.numpy())
+    q = torch.empty((37, 301), dtype=torch.int8, device=DEV)
+    s = torch.empty(37, dtype=torch.float32, device=DEV)
+    check(backend, backend.library().ss_weight_grid_device(ptr(w.to(DEV)), 37, 301, ptr(q), ptr(s), stream()))
+    assert np.array_equal(s.cpu().numpy(), s_ref) and np.array_equal(q.cpu().numpy(), q_ref)
