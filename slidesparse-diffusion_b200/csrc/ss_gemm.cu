@@ -9,11 +9,18 @@
 // and its columns are tokens, as in the reference (csrc/dualscale_sm80.cu:189-204).
 //
 // One persistent CTA per SM, 6 warps:
-//   warp 0     TMA producer: per 128-wide lifted-K block one load each of A (128 x 64 B, 64B
-//              swizzle), B (NT x 128 B, 128B swizzle) and the metadata block (128 x 16 B)
-//   warp 1     owns tensor memory; one lane copies the metadata block to TMEM (tcgen05.cp) and
-//              issues two K=64 tcgen05.mma.sp per stage, commits to the stage's empty barrier
-//   warps 2-5  epilogue: tcgen05.ld of their 32-lane quadrant, dequantise, store BF16
+//   warp 0     TMA producer.  A pipeline stage holds KB blocks of 128 lifted columns (KB = 2
+//              wherever shared memory allows): one load of A (128 rows x 64*KB bytes), and per
+//              block one load of B (NT rows x 128 B, 128B swizzle) and of metadata (128 x 16 B)
+//   warp 1     owns tensor memory; one lane copies the metadata blocks to TMEM (tcgen05.cp),
+//              issues 2*KB tcgen05.mma.sp (K = 64 each) per stage and commits to the stage's
+//              empty barrier.  The tensor pipe accepts little work ahead of what it executes,
+//              so everything else this lane does between two MMAs (barrier wait, commit) leaves
+//              the pipe idle: stages are as large as they can be and the next stage's barrier
+//              is tested before the current stage's MMAs are issued.
+//   warps 2-5  epilogue: token scales of the tile are staged in shared memory before the
+//              accumulator is ready; tcgen05.ld of the warp's 32-lane quadrant is double
+//              buffered, the TMEM buffer is handed back as soon as the last load has landed.
 // Accumulators are double-buffered in TMEM when the token tile leaves room (NT <= 192), so the
 // epilogue of tile i overlaps the main loop of tile i+1.  Every mbarrier wait is bounded; a
 // wait that runs out records a code in the device status word and the CTA winds down.
@@ -31,25 +38,29 @@ namespace {
 
 constexpr int kThreads = 192;
 constexpr int kTileCh = 128;                     // UMMA M
-constexpr int kTileK = 128;                      // lifted K per stage
-constexpr int kABytes = kTileCh * kTileK / 2;    // compressed weights per stage
-constexpr int kEBytes = kTileCh * kTileK / 8;    // metadata per stage
+constexpr int kBlockK = 128;                     // lifted columns per metadata / B block
 constexpr int kTmemCols = 512;
-constexpr int kMetaColsPerStage = 4;
 
-template <int NT>
+template <int NT, int KB>
 struct Tile {
-  static constexpr int kBBytes = NT * kTileK;
+  static constexpr int kABytes = kTileCh * (kBlockK / 2) * KB;   // compressed weights per stage
+  static constexpr int kBBlock = NT * kBlockK;                    // one B block
+  static constexpr int kBBytes = kBBlock * KB;
+  static constexpr int kEBlock = kTileCh * kBlockK / 8;           // one metadata block (2 KB)
+  static constexpr int kEBytes = kEBlock * KB;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;
-  static constexpr int kStagesRaw = (214 * 1024) / kStageBytes;
+  static constexpr int kStagesRaw = (212 * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kMetaColsPerStage = 4 * KB;
   static constexpr int kAccBufs = (kTmemCols - kStages * kMetaColsPerStage) / NT >= 2 ? 2 : 1;
   static constexpr int kMetaCol = kAccBufs * NT;             // first metadata column
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + kStages * kABytes;
   static constexpr int kOffE = kOffB + kStages * kBBytes;
-  static constexpr int kOffBar = kOffE + kStages * kEBytes;
+  static constexpr int kOffSa = kOffE + kStages * kEBytes;   // 4 warps x NT token scales
+  static constexpr int kOffBar = kOffSa + 4 * NT * 4;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;    // + barrier block + alignment slack
+  static_assert(kStages >= 2, "pipeline depth");
   static_assert(kMetaCol + kStages * kMetaColsPerStage <= kTmemCols, "TMEM budget");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
   static_assert(NT % 32 == 0 && NT >= 32 && NT <= 256, "token tile");
@@ -78,12 +89,55 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-template <int NT, bool INT32_OUT, bool HAS_ADDEND>
+__device__ __forceinline__ bool mbar_peek(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok)
+      : "r"(ptx::smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Dequantise one 32-token chunk held in registers (lane = channel) and store it.
+template <bool INT32_OUT, bool HAS_ADDEND>
+__device__ __forceinline__ void store_chunk(const uint32_t (&r)[32], const KernelArgs& args,
+                                            const float* sa_chunk, int tok_base, int ch, bool ch_ok,
+                                            float sw, float bias) {
+  if constexpr (INT32_OUT) {
+    int32_t* out = static_cast<int32_t*>(args.out);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (ch_ok && tok_base + j < args.m)
+        out[static_cast<long long>(tok_base + j) * args.out_stride + ch] = static_cast<int32_t>(r[j]);
+  } else {
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out);
+#pragma unroll
+    for (int j4 = 0; j4 < 8; ++j4) {
+      const float4 s4 = reinterpret_cast<const float4*>(sa_chunk)[j4];
+      const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j4 * 4 + jj, tok = tok_base + j;
+        float y = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[j])), __fmul_rn(sv[jj], sw), bias);
+        if (ch_ok && tok < args.m) {
+          if constexpr (HAS_ADDEND)
+            y = __fadd_rn(y, __bfloat162float(args.addend[static_cast<long long>(tok) * args.addend_stride + ch]));
+          out[static_cast<long long>(tok) * args.out_stride + ch] = __float2bfloat16_rn(y);
+        }
+      }
+    }
+  }
+}
+
+template <int NT, int KB, bool INT32_OUT, bool HAS_ADDEND>
 __global__ void __launch_bounds__(kThreads, 1)
 sparse_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                    const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_e, const KernelArgs args) {
-  using T = Tile<NT>;
+  using T = Tile<NT, KB>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -95,6 +149,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = args.tiles_ch * args.tiles_tok;
+  const int num_st = (args.num_kb + KB - 1) / KB;          // pipeline stages per tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T::kStages; ++s) {
@@ -127,13 +182,20 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int ch0 = (tile % args.tiles_ch) * kTileCh;
         const int tok0 = (tile / args.tiles_ch) * NT;
-        for (int kb = 0; kb < args.num_kb; ++kb, ++issued) {
+        for (int st = 0; st < num_st; ++st, ++issued) {
           const uint32_t s = issued % T::kStages, use = issued / T::kStages;
+          const int kb0 = st * KB;
+          const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
           if (!ptx::mbar_wait(&bar_empty[s], (use & 1u) ^ 1u)) { ok = false; break; }
-          ptx::mbar_arrive_expect_tx(&bar_full[s], T::kStageBytes);
-          ptx::tma_load_2d(smem + T::kOffA + s * kABytes, &map_a, &bar_full[s], kb * (kTileK / 2), ch0);
-          ptx::tma_load_2d(smem + T::kOffB + s * T::kBBytes, &map_b, &bar_full[s], kb * kTileK, tok0);
-          ptx::tma_load_3d(smem + T::kOffE + s * kEBytes, &map_e, &bar_full[s], 0, kb, ch0 >> 5);
+          ptx::mbar_arrive_expect_tx(&bar_full[s], T::kABytes + nkb * (T::kBBlock + T::kEBlock));
+          // the A box always spans KB blocks; columns past the row end arrive as zeros
+          ptx::tma_load_2d(smem + T::kOffA + s * T::kABytes, &map_a, &bar_full[s], kb0 * (kBlockK / 2), ch0);
+          for (int h = 0; h < nkb; ++h) {
+            ptx::tma_load_2d(smem + T::kOffB + s * T::kBBytes + h * T::kBBlock, &map_b, &bar_full[s],
+                             (kb0 + h) * kBlockK, tok0);
+            ptx::tma_load_3d(smem + T::kOffE + s * T::kEBytes + h * T::kEBlock, &map_e, &bar_full[s], 0,
+                             kb0 + h, ch0 >> 5);
+          }
         }
       }
       if (!ok) {
@@ -153,28 +215,36 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                  | (1u << 7) | (1u << 10)  // A, B format: signed 8-bit
                                  | (static_cast<uint32_t>(NT >> 3) << 17) |
                                  (static_cast<uint32_t>(kTileCh >> 4) << 24);
+      // A rows are 64*KB bytes: 64B swizzle (8 rows = 512 B) or 128B swizzle (8 rows = 1024 B)
+      constexpr uint32_t a_layout = KB == 2 ? 2u : 4u, a_sbo = KB == 2 ? 1024u : 512u;
       uint32_t consumed = 0, acc_it = 0;
-      bool ok = true;
+      bool ok = true, ready = false;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
         const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
         if (!ptx::mbar_wait(&bar_acc_empty[buf], (acc_use & 1u) ^ 1u)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * NT;
-        for (int kb = 0; kb < args.num_kb; ++kb, ++consumed) {
+        for (int st = 0; st < num_st; ++st, ++consumed) {
           const uint32_t s = consumed % T::kStages, use = consumed / T::kStages;
-          if (!ptx::mbar_wait(&bar_full[s], use & 1u)) { ok = false; break; }
+          const int kb0 = st * KB;
+          const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
+          if (!ready && !ptx::mbar_wait(&bar_full[s], use & 1u)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint32_t a_addr = ptx::smem_u32(smem + T::kOffA + s * kABytes);
+          const uint32_t a_addr = ptx::smem_u32(smem + T::kOffA + s * T::kABytes);
           const uint32_t b_addr = ptx::smem_u32(smem + T::kOffB + s * T::kBBytes);
-          const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * kEBytes);
-          const uint32_t e_tmem = tmem_base + T::kMetaCol + s * kMetaColsPerStage;
-          ptx::tc_cp_128x128b(e_tmem, smem_desc(e_addr, 128, 128, 0));
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
+          const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
+          const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
+          for (int h = 0; h < nkb; ++h)
+            ptx::tc_cp_128x128b(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+          {  // look at the next stage's barrier while the pipe is still busy
+            const uint32_t s2 = (consumed + 1) % T::kStages, use2 = (consumed + 1) / T::kStages;
+            ready = mbar_peek(&bar_full[s2], use2 & 1u);
+          }
+          for (int j = 0; j < 2 * nkb; ++j) {
             // K = 64 lifted columns per instruction: 32 B of compressed A, 64 B of B per row
-            const uint64_t adesc = smem_desc(a_addr + j * 32, 16, 512, 4);
-            const uint64_t bdesc = smem_desc(b_addr + j * 64, 16, 1024, 2);
-            ptx::tc_mma_sp_i8(d_tmem, adesc, bdesc, e_tmem + j * 2, idesc, (kb | j) != 0 ? 1u : 0u);
+            const uint64_t adesc = smem_desc(a_addr + j * 32, 16, a_sbo, a_layout);
+            const uint64_t bdesc = smem_desc(b_addr + (j >> 1) * T::kBBlock + (j & 1) * 64, 16, 1024, 2);
+            ptx::tc_mma_sp_i8(d_tmem, adesc, bdesc, e_tmem + j * 2, idesc, (st | j) != 0 ? 1u : 0u);
           }
           ptx::tc_commit(&bar_empty[s]);
         }
@@ -185,6 +255,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+    float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
     uint32_t acc_it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++acc_it) {
@@ -194,48 +265,38 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const bool ch_ok = ch < args.n;
       float sw = 1.f, bias = 0.f;
       if constexpr (!INT32_OUT) {
+        // stage this tile's token scales while the main loop is still running
+        __syncwarp();
+        for (int i = lane; i < NT; i += 32) sa_s[i] = tok0 + i < args.m ? __ldg(args.sa + tok0 + i) : 1.f;
         if (ch_ok) {
           sw = __ldg(args.sw + ch);
           if (args.bias) bias = __ldg(args.bias + ch);
         }
+        __syncwarp();
       }
+      int chunks = (args.m - tok0 + 31) / 32;
+      chunks = chunks < NT / 32 ? chunks : NT / 32;
       if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u)) { ok = false; break; }
       ptx::tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * NT;
+      auto release = [&]() {                         // every load has landed: hand the buffer back
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[buf]);
+      };
+      uint32_t r0[32], r1[32];
+      ptx::tc_ld_32x32b_x32(t_addr, r0);
 #pragma unroll 1
-      for (int c = 0; c < NT / 32; ++c) {
-        const int tok_base = tok0 + c * 32;
-        if (tok_base >= args.m) break;
-        uint32_t r[32];
-        ptx::tc_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * NT + c * 32, r);
+      for (int c = 0; c < chunks; c += 2) {
         ptx::tc_wait_ld();
-        if constexpr (INT32_OUT) {
-          int32_t* out = static_cast<int32_t*>(args.out);
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (ch_ok && tok_base + j < args.m)
-              out[static_cast<long long>(tok_base + j) * args.out_stride + ch] = static_cast<int32_t>(r[j]);
-        } else {
-          __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out);
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 s4 = __ldg(reinterpret_cast<const float4*>(args.sa + tok_base) + j4);
-            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              const int j = j4 * 4 + jj, tok = tok_base + j;
-              float y = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[j])), __fmul_rn(sv[jj], sw), bias);
-              if (ch_ok && tok < args.m) {
-                if constexpr (HAS_ADDEND)
-                  y = __fadd_rn(y, __bfloat162float(args.addend[static_cast<long long>(tok) * args.addend_stride + ch]));
-                out[static_cast<long long>(tok) * args.out_stride + ch] = __float2bfloat16_rn(y);
-              }
-            }
-          }
+        if (c + 1 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 1) * 32, r1); else release();
+        store_chunk<INT32_OUT, HAS_ADDEND>(r0, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
+        if (c + 1 < chunks) {
+          ptx::tc_wait_ld();
+          if (c + 2 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 2) * 32, r0); else release();
+          store_chunk<INT32_OUT, HAS_ADDEND>(r1, args, sa_s + (c + 1) * 32, tok0 + (c + 1) * 32, ch, ch_ok, sw, bias);
         }
       }
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&bar_acc_empty[buf]);
     }
     if (!ok && lane == 0) atomicOr(args.status, kStatusEpilogueTimeout);
   }
@@ -248,6 +309,8 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
 }
+
+#include "ss_gemm_pair.cuh"
 
 // ---- host side -----------------------------------------------------------------------------
 
@@ -281,7 +344,7 @@ int encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* bas
   return SS_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool configured[4][2][2] = {}; };
+struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][2][2] = {}; };
 DeviceInfo* device_info() {
   static std::mutex mu;
   static std::unordered_map<int, DeviceInfo> table;
@@ -301,7 +364,7 @@ int pick_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
     if (v == 64 || v == 128 || v == 192 || v == 256) return v;
   }
   const int64_t tiles_ch = (pn + kTileCh - 1) / kTileCh;
-  const double num_kb = static_cast<double>(pk / kTileK);
+  const double num_kb = static_cast<double>(pk / kBlockK);
   const int cand[4] = {256, 192, 128, 64};
   // shared-memory operand traffic per MMA relative to the 256-token tile
   const double feed[4] = {1.0, 1.0625, 1.2, 1.6};
@@ -322,10 +385,10 @@ int pick_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   return best_nt;
 }
 
-template <int NT, bool I32, bool ADD>
+template <int NT, int KB, bool I32, bool ADD>
 int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
-  using T = Tile<NT>;
-  auto kernel = sparse_gemm_kernel<NT, I32, ADD>;
+  using T = Tile<NT, KB>;
+  auto kernel = sparse_gemm_kernel<NT, KB, I32, ADD>;
   if (!dev->configured[cfg_index][I32][ADD]) {
     SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
     dev->configured[cfg_index][I32][ADD] = true;
@@ -334,19 +397,20 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.pk / 2), static_cast<cuuint64_t>(a.pn)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.pk / 2)};
-    const cuuint32_t box[2] = {kTileK / 2, kTileCh};
-    int rc = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.packed, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    const cuuint32_t box[2] = {kBlockK / 2 * KB, kTileCh};
+    int rc = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.packed, dims, strides, box,
+                    KB == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
   }
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.pk), static_cast<cuuint64_t>(a.pm)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.pk)};
-    const cuuint32_t box[2] = {kTileK, NT};
+    const cuuint32_t box[2] = {kBlockK, NT};
     int rc = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
   {
-    const cuuint64_t kblocks = static_cast<cuuint64_t>(a.pk / kTileK);
+    const cuuint64_t kblocks = static_cast<cuuint64_t>(a.pk / kBlockK);
     const cuuint64_t dims[3] = {128, kblocks, static_cast<cuuint64_t>(a.pn / 32)};
     const cuuint64_t strides[2] = {512, kblocks * 512};
     const cuuint32_t box[3] = {128, 1, 4};
@@ -361,7 +425,7 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   k.m = static_cast<int>(a.m); k.n = static_cast<int>(a.n);
   k.tiles_ch = static_cast<int>((a.pn + kTileCh - 1) / kTileCh);
   k.tiles_tok = static_cast<int>((a.m + NT - 1) / NT);
-  k.num_kb = static_cast<int>(a.pk / kTileK);
+  k.num_kb = static_cast<int>(a.pk / kBlockK);
   k.status = device_status_ptr();
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
   const int64_t tiles = static_cast<int64_t>(k.tiles_ch) * k.tiles_tok;
@@ -371,11 +435,77 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   return SS_OK;
 }
 
-template <int NT>
+template <int NT, int KB>
 int launch_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
-  if (a.int32_out) return launch_t<NT, true, false>(a, dev, cfg_index, stream);
-  if (a.addend) return launch_t<NT, false, true>(a, dev, cfg_index, stream);
-  return launch_t<NT, false, false>(a, dev, cfg_index, stream);
+  if (a.int32_out) return launch_t<NT, KB, true, false>(a, dev, cfg_index, stream);
+  if (a.addend) return launch_t<NT, KB, false, true>(a, dev, cfg_index, stream);
+  return launch_t<NT, KB, false, false>(a, dev, cfg_index, stream);
+}
+
+// ---- CTA-pair launcher -----------------------------------------------------------------------
+template <int NT, int KB, bool I32, bool ADD>
+int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
+  using T = PairTile<NT, KB>;
+  auto kernel = sparse_gemm_pair_kernel<NT, KB, I32, ADD>;
+  if (!dev->pair_configured[cfg_index][I32][ADD]) {
+    SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
+    dev->pair_configured[cfg_index][I32][ADD] = true;
+  }
+  CUtensorMap map_a, map_b, map_e;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.pk / 2), static_cast<cuuint64_t>(a.pn)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.pk / 2)};
+    const cuuint32_t box[2] = {kBlockK / 2 * KB, kTileCh};
+    int rc = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.packed, dims, strides, box,
+                    KB == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+  }
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.pk), static_cast<cuuint64_t>(a.pm)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.pk)};
+    const cuuint32_t box[2] = {kBlockK, T::kHalf};          // each CTA loads half of the token rows
+    int rc = encode(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.q, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  {
+    const cuuint64_t kblocks = static_cast<cuuint64_t>(a.pk / kBlockK);
+    const cuuint64_t dims[3] = {128, kblocks, static_cast<cuuint64_t>(a.pn / 32)};
+    const cuuint64_t strides[2] = {512, kblocks * 512};
+    const cuuint32_t box[3] = {128, 1, 4};
+    int rc = encode(&map_e, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, a.meta, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  }
+  KernelArgs k;
+  k.sa = a.sa; k.sw = a.sw; k.bias = a.bias;
+  k.addend = static_cast<const __nv_bfloat16*>(a.addend);
+  k.addend_stride = a.addend_stride;
+  k.out = a.out; k.out_stride = a.out_stride;
+  k.m = static_cast<int>(a.m); k.n = static_cast<int>(a.n);
+  k.tiles_ch = static_cast<int>((a.pn + kTileCh - 1) / kTileCh);
+  k.tiles_tok = static_cast<int>((a.m + NT - 1) / NT);
+  k.num_kb = static_cast<int>(a.pk / kBlockK);
+  k.status = device_status_ptr();
+  SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
+  const int64_t tiles = static_cast<int64_t>((k.tiles_ch + 1) / 2) * k.tiles_tok;
+  const int64_t pairs = dev->sms / 2;
+  const unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);
+  kernel<<<grid, kThreads, T::kSmemBytes, stream>>>(map_a, map_b, map_e, k);
+  SS_CUDA(cudaGetLastError());
+  return SS_OK;
+}
+
+template <int NT, int KB>
+int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
+  if (a.int32_out) return launch_pair_t<NT, KB, true, false>(a, dev, cfg_index, stream);
+  if (a.addend) return launch_pair_t<NT, KB, false, true>(a, dev, cfg_index, stream);
+  return launch_pair_t<NT, KB, false, false>(a, dev, cfg_index, stream);
+}
+
+// Blocks of 128 lifted columns per pipeline stage: 2 wherever at least 3 stages still fit.
+int stage_blocks(int nt) {
+  if (nt != 256) return 2;
+  const char* env = std::getenv("SS_STAGE_BLOCKS");
+  return env && std::atoi(env) == 2 ? 2 : 1;
 }
 
 int check_args(const GemmArgs& a) {
@@ -403,18 +533,30 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (int rc = check_args(a)) return rc;
   DeviceInfo* dev = device_info();
   SS_REQUIRE(dev, SS_E_CUDA, "gemm: no current CUDA device");
-  switch (pick_token_tile(a.m, a.pn, a.pk, dev->sms)) {
-    case 256: return launch_nt<256>(a, dev, 0, stream);
-    case 192: return launch_nt<192>(a, dev, 1, stream);
-    case 128: return launch_nt<128>(a, dev, 2, stream);
-    default:  return launch_nt<64>(a, dev, 3, stream);
+  if (const char* env = std::getenv("SS_PAIR")) {
+    if (std::atoi(env) == 1) {
+      const char* t = std::getenv("SS_TOKEN_TILE");
+      switch (t ? std::atoi(t) : 256) {
+        case 128: return launch_pair_nt<128, 2>(a, dev, 0, stream);
+        case 192: return launch_pair_nt<192, 2>(a, dev, 1, stream);
+        case 224: return launch_pair_nt<224, 2>(a, dev, 2, stream);
+        default:  return launch_pair_nt<256, 2>(a, dev, 3, stream);
+      }
+    }
+  }
+  const int nt = pick_token_tile(a.m, a.pn, a.pk, dev->sms);
+  switch (nt) {
+    case 256: return stage_blocks(nt) == 2 ? launch_nt<256, 2>(a, dev, 4, stream) : launch_nt<256, 1>(a, dev, 0, stream);
+    case 192: return launch_nt<192, 2>(a, dev, 1, stream);
+    case 128: return launch_nt<128, 2>(a, dev, 2, stream);
+    default:  return launch_nt<64, 2>(a, dev, 3, stream);
   }
 }
 
-template <int NT>
+template <int NT, int KB>
 static int resources_t(GemmResources* r) {
-  using T = Tile<NT>;
-  auto kernel = sparse_gemm_kernel<NT, false, false>;
+  using T = Tile<NT, KB>;
+  auto kernel = sparse_gemm_kernel<NT, KB, false, false>;
   cudaFuncAttributes attr;
   SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
   SS_CUDA(cudaFuncGetAttributes(&attr, kernel));
@@ -429,11 +571,12 @@ static int resources_t(GemmResources* r) {
 int gemm_resources(int64_t m, int64_t n, int64_t pk, GemmResources* r) {
   DeviceInfo* dev = device_info();
   SS_REQUIRE(dev, SS_E_CUDA, "gemm: no current CUDA device");
-  switch (pick_token_tile(m, ceil_to(n, 32), pk, dev->sms)) {
-    case 256: return resources_t<256>(r);
-    case 192: return resources_t<192>(r);
-    case 128: return resources_t<128>(r);
-    default:  return resources_t<64>(r);
+  const int nt = pick_token_tile(m, ceil_to(n, 32), pk, dev->sms);
+  switch (nt) {
+    case 256: return stage_blocks(nt) == 2 ? resources_t<256, 2>(r) : resources_t<256, 1>(r);
+    case 192: return resources_t<192, 2>(r);
+    case 128: return resources_t<128, 2>(r);
+    default:  return resources_t<64, 2>(r);
   }
 }
 

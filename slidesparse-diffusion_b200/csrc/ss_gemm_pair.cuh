@@ -1,0 +1,219 @@
+// CTA-pair variant of the sparse GEMM (tcgen05 cta_group::2).  Included by ss_gemm.cu inside
+// namespace ss::{anonymous}, after KernelArgs, smem_desc, mbar_peek and store_chunk.
+//
+// Why a pair: the single-CTA kernel is bound by shared-memory bandwidth, not by the tensor
+// pipe.  A K=64 sparse INT8 MMA of M=128 x N reads 4 KB of A and 64*N bytes of B from shared
+// memory, and TMA wrote the same bytes there a moment earlier; at 128 B/clk for reads and writes
+// together that is 2*(5 KB + 64*N) / 128 cycles against N/2 cycles of tensor work (36 % of the
+// tensor peak at N = 192).  With cta_group::2 the two CTAs of a cluster compute 256 channels x N
+// tokens together: each CTA stores and reads its own 128 channel rows of A and only HALF of the
+// token rows of B (the hardware hands each half to the peer SM), which halves the dominant B
+// traffic (61 % at N = 256, 58 % at N = 224).  No multicast load is involved.
+//
+// Protocol (rank = %cluster_ctarank):
+//   full[s]      lives in rank 0 only.  Rank 0's producer posts the byte count of BOTH CTAs'
+//                loads; both producers issue their loads with the cta_group::2 form, which
+//                credits completion to rank 0's barrier.
+//   empty[s]     one copy per CTA; the MMA thread (rank 0) commits with a 2-CTA multicast so
+//                both producers see the stage free at the same time.
+//   acc_full[b]  one copy per CTA, multicast commit; acc_empty[b] lives in rank 0 and counts the
+//                8 epilogue warps of the pair (rank 1 arrives through shared::cluster).
+#pragma once
+
+template <int NT, int KB>
+struct PairTile {
+  static constexpr int kHalf = NT / 2;                             // B token rows held per CTA
+  static constexpr int kABytes = kTileCh * (kBlockK / 2) * KB;
+  static constexpr int kBBlock = kHalf * kBlockK;
+  static constexpr int kBBytes = kBBlock * KB;
+  static constexpr int kEBlock = kTileCh * kBlockK / 8;
+  static constexpr int kEBytes = kEBlock * KB;
+  static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;  // per CTA
+  static constexpr int kStagesRaw = (212 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kMetaColsPerStage = 4 * KB;
+  static constexpr int kAccBufs = (kTmemCols - kStages * kMetaColsPerStage) / NT >= 2 ? 2 : 1;
+  static constexpr int kMetaCol = kAccBufs * NT;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kOffA + kStages * kABytes;
+  static constexpr int kOffE = kOffB + kStages * kBBytes;
+  static constexpr int kOffSa = kOffE + kStages * kEBytes;
+  static constexpr int kOffBar = kOffSa + 4 * NT * 4;
+  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static_assert(kStages >= 2, "pipeline depth");
+  static_assert(kMetaCol + kStages * kMetaColsPerStage <= kTmemCols, "TMEM budget");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+  static_assert(NT % 32 == 0 && NT >= 64 && NT <= 256, "token tile of a CTA pair");
+  static_assert(kBBlock % 1024 == 0, "B blocks must keep the 128B-swizzle alignment");
+};
+
+template <int NT, int KB, bool INT32_OUT, bool HAS_ADDEND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                        const __grid_constant__ CUtensorMap map_b,
+                        const __grid_constant__ CUtensorMap map_e, const KernelArgs args) {
+  using T = PairTile<NT, KB>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + T::kOffBar);
+  uint64_t* bar_empty = bar_full + T::kStages;
+  uint64_t* bar_acc_full = bar_empty + T::kStages;
+  uint64_t* bar_acc_empty = bar_acc_full + T::kAccBufs;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + T::kAccBufs);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int tiles_ch2 = (args.tiles_ch + 1) >> 1;            // tiles of 256 channels
+  const int num_tiles = tiles_ch2 * args.tiles_tok;
+  const int num_st = (args.num_kb + KB - 1) / KB;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::kStages; ++s) {
+      ptx::mbar_init(&bar_full[s], 1);
+      ptx::mbar_init(&bar_empty[s], 1);
+    }
+    for (int b = 0; b < T::kAccBufs; ++b) {
+      ptx::mbar_init(&bar_acc_full[b], 1);
+      ptx::mbar_init(&bar_acc_empty[b], 8);
+    }
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+    ptx::prefetch_tensormap(&map_e);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();            // the peer's barriers exist before anything is signalled there
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t issued = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int ch0 = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
+        const int tok0 = (tile / tiles_ch2) * NT + static_cast<int>(rank) * T::kHalf;
+        for (int st = 0; st < num_st; ++st, ++issued) {
+          const uint32_t s = issued % T::kStages, use = issued / T::kStages;
+          const int kb0 = st * KB;
+          const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
+          if (!ptx::mbar_wait(&bar_empty[s], (use & 1u) ^ 1u)) { ok = false; break; }
+          if (rank == 0)
+            ptx::mbar_arrive_expect_tx(&bar_full[s], 2 * (T::kABytes + nkb * (T::kBBlock + T::kEBlock)));
+          ptx::tma_load_2d_pair(smem + T::kOffA + s * T::kABytes, &map_a, &bar_full[s], kb0 * (kBlockK / 2), ch0);
+          for (int h = 0; h < nkb; ++h) {
+            ptx::tma_load_2d_pair(smem + T::kOffB + s * T::kBBytes + h * T::kBBlock, &map_b, &bar_full[s],
+                                  (kb0 + h) * kBlockK, tok0);
+            ptx::tma_load_3d_pair(smem + T::kOffE + s * T::kEBytes + h * T::kEBlock, &map_e, &bar_full[s], 0,
+                                  kb0 + h, ch0 >> 5);
+          }
+        }
+      }
+      if (!ok) atomicOr(args.status, kStatusProducerTimeout);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (rank 0 only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = (1u << 2) | (2u << 4) | (1u << 7) | (1u << 10) |
+                                 (static_cast<uint32_t>(NT >> 3) << 17) |
+                                 (static_cast<uint32_t>((2 * kTileCh) >> 4) << 24);
+      constexpr uint32_t a_layout = KB == 2 ? 2u : 4u, a_sbo = KB == 2 ? 1024u : 512u;
+      uint32_t consumed = 0, acc_it = 0;
+      bool ok = true, ready = false;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
+        const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
+        if (!ptx::mbar_wait(&bar_acc_empty[buf], (acc_use & 1u) ^ 1u)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * NT;
+        for (int st = 0; st < num_st; ++st, ++consumed) {
+          const uint32_t s = consumed % T::kStages, use = consumed / T::kStages;
+          const int kb0 = st * KB;
+          const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
+          if (!ready && !ptx::mbar_wait(&bar_full[s], use & 1u)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = ptx::smem_u32(smem + T::kOffA + s * T::kABytes);
+          const uint32_t b_addr = ptx::smem_u32(smem + T::kOffB + s * T::kBBytes);
+          const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
+          const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
+          for (int h = 0; h < nkb; ++h)
+            ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+          {
+            const uint32_t s2 = (consumed + 1) % T::kStages, use2 = (consumed + 1) / T::kStages;
+            ready = mbar_peek(&bar_full[s2], use2 & 1u);
+          }
+          for (int j = 0; j < 2 * nkb; ++j) {
+            const uint64_t adesc = smem_desc(a_addr + j * 32, 16, a_sbo, a_layout);
+            const uint64_t bdesc = smem_desc(b_addr + (j >> 1) * T::kBBlock + (j & 1) * 64, 16, 1024, 2);
+            ptx::tc_mma_sp_i8_pair(d_tmem, adesc, bdesc, e_tmem + j * 2, idesc, (st | j) != 0 ? 1u : 0u);
+          }
+          ptx::tc_commit_pair(&bar_empty[s], 3);
+        }
+        if (ok) ptx::tc_commit_pair(&bar_acc_full[buf], 3);
+      }
+      if (!ok) atomicOr(args.status, kStatusMmaTimeout);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quad = warp & 3;
+    float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
+      const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
+      const int ch = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
+      const int tok0 = (tile / tiles_ch2) * NT;
+      const bool ch_ok = ch < args.n;
+      float sw = 1.f, bias = 0.f;
+      if constexpr (!INT32_OUT) {
+        __syncwarp();
+        for (int i = lane; i < NT; i += 32) sa_s[i] = tok0 + i < args.m ? __ldg(args.sa + tok0 + i) : 1.f;
+        if (ch_ok) {
+          sw = __ldg(args.sw + ch);
+          if (args.bias) bias = __ldg(args.bias + ch);
+        }
+        __syncwarp();
+      }
+      int chunks = (args.m - tok0 + 31) / 32;
+      chunks = chunks < NT / 32 ? chunks : NT / 32;
+      if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u)) { ok = false; break; }
+      ptx::tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * NT;
+      auto release = [&]() {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_rank0(&bar_acc_empty[buf]);
+      };
+      uint32_t r0[32], r1[32];
+      ptx::tc_ld_32x32b_x32(t_addr, r0);
+#pragma unroll 1
+      for (int c = 0; c < chunks; c += 2) {
+        ptx::tc_wait_ld();
+        if (c + 1 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 1) * 32, r1); else release();
+        store_chunk<INT32_OUT, HAS_ADDEND>(r0, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
+        if (c + 1 < chunks) {
+          ptx::tc_wait_ld();
+          if (c + 2 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 2) * 32, r0); else release();
+          store_chunk<INT32_OUT, HAS_ADDEND>(r1, args, sa_s + (c + 1) * 32, tok0 + (c + 1) * 32, ch, ch_ok, sw, bias);
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicOr(args.status, kStatusEpilogueTimeout);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();            // neither CTA leaves while the peer may still touch its memory
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
