@@ -1,16 +1,19 @@
 // Front-end: dynamic per-token INT8 quantisation + slide expansion, one pass over HBM.
 //
-// One CTA per token row.  The row is read once with 128-bit loads and kept in registers
-// (up to kMaxVec 16-byte vectors per thread), the absolute maximum is reduced with warp shuffles
-// (plus one shared-memory hop between warps), and the row is quantised from the registers.
-// For 2:4 the quantised bytes go straight to global memory; for 4:6 / 6:8 they pass through a
-// shared-memory copy of the row from which every thread assembles 16-byte vectors of the
-// overlapping-window layout, so the lifted row is written with full 16-byte stores.
+// One CTA per token row.  A thread owns whole "chunks" of the row: CV consecutive 16-byte vectors
+// (2 for 2:4, 3 for 4:6, 4 for 6:8), i.e. a whole number of groups whose slide-expanded image is a
+// whole number of 16-byte vectors (16 -> 16, 24 -> 32, 32 -> 48 bytes).  The row is read once with
+// 128-bit loads into registers, the absolute maximum is taken on the BF16 bit patterns (packed
+// 16-bit integer max, one instruction per two elements) and reduced with warp shuffles plus one
+// shared-memory hop, the row is quantised from the registers, the overlapping windows are cut
+// out of the thread's own quantised bytes with funnel shifts, and written with 128-bit stores.
+// No shared-memory staging of data, no re-read of x.
 //
 // Arithmetic follows the reference statement of the front-end exactly
-// (csrc/projection_sm80.cu:8-88): fmaxf absmax that ignores NaN, two IEEE divisions, an fp32
-// multiply by the reciprocal, clamp to [-128,127], round-half-even; rows m..pm-1 are zero with
-// scale 1.  No fast-math.
+// (csrc/projection_sm80.cu:8-88): absmax that ignores NaN, two IEEE divisions, an fp32 multiply
+// by the reciprocal, clamp to [-128,127], round-half-even; rows m..pm-1 are zero with scale 1.
+// Rows that contain Inf or NaN (detected from the same packed maximum) take an element-wise path
+// that reproduces the reference's fmaxf/fminf conventions bit for bit.  No fast-math.
 #include "ss_common.cuh"
 
 namespace ss {
@@ -21,14 +24,41 @@ constexpr int kMaxThreads = 512;
 
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
-__device__ __forceinline__ uint32_t quant1(float v, float inv) {
-  return static_cast<uint32_t>(__float2int_rn(fminf(127.f, fmaxf(-128.f, __fmul_rn(v, inv))))) &
-         255u;
+
+// Reference element rule, used for rows with non-finite values.
+__device__ __forceinline__ uint32_t quant_exact(float v, float inv) {
+  return static_cast<uint32_t>(__float2int_rn(fminf(127.f, fmaxf(-128.f, __fmul_rn(v, inv))))) & 255u;
 }
-__device__ __forceinline__ uint32_t quant_pair_lo(uint32_t a, uint32_t b, float inv) {
-  // four consecutive bf16 (two packed words) -> four int8 in one word
-  return quant1(bf_lo(a), inv) | (quant1(bf_hi(a), inv) << 8) | (quant1(bf_lo(b), inv) << 16) |
-         (quant1(bf_hi(b), inv) << 24);
+__device__ __forceinline__ uint32_t quant4_exact(uint32_t a, uint32_t b, float inv) {
+  return quant_exact(bf_lo(a), inv) | (quant_exact(bf_hi(a), inv) << 8) |
+         (quant_exact(bf_lo(b), inv) << 16) | (quant_exact(bf_hi(b), inv) << 24);
+}
+// Finite rows: round to nearest even, then saturate while packing (same result as clamp-then-round).
+__device__ __forceinline__ uint32_t quant4_fast(uint32_t a, uint32_t b, float inv) {
+  const int i0 = __float2int_rn(__fmul_rn(bf_lo(a), inv)), i1 = __float2int_rn(__fmul_rn(bf_hi(a), inv));
+  const int i2 = __float2int_rn(__fmul_rn(bf_lo(b), inv)), i3 = __float2int_rn(__fmul_rn(bf_hi(b), inv));
+  uint32_t hi, out;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(i3), "r"(i2), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(i1), "r"(i0), "r"(hi));
+  return out;
+}
+
+template <int L> struct Chunk;
+template <> struct Chunk<4> { static constexpr int kVec = 2, kOutWords = 4; };
+template <> struct Chunk<6> { static constexpr int kVec = 3, kOutWords = 8; };
+template <> struct Chunk<8> { static constexpr int kVec = 4, kOutWords = 12; };
+
+// Lifted words of one chunk from its quantised words (all indices are compile-time constants).
+template <int L>
+__device__ __forceinline__ void lift_chunk(const uint32_t* qw, uint32_t* ow) {
+  constexpr int W = L / 2 - 1, kGroups = Chunk<L>::kVec * 8 / L;
+#pragma unroll
+  for (int g = 0; g < kGroups; ++g)
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const int o = g * L + 2 * j;                           // byte offset of the window
+      ow[g * W + j] = (o & 3) ? __funnelshift_r(qw[o >> 2], qw[(o >> 2) + 1], 16) : qw[o >> 2];
+    }
 }
 
 // L: group size (4, 6, 8).  VEC: rows are 16-byte aligned and k % 8 == 0.
@@ -36,99 +66,107 @@ template <int L, bool VEC>
 __global__ void __launch_bounds__(kMaxThreads)
 quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict__ q,
                   float* __restrict__ sa, int m, int k, int pk, int nvec) {
-  extern __shared__ __align__(16) uint8_t qs[];   // L != 4: quantised row, un-lifted
-  __shared__ float warp_max[32];
+  constexpr int CV = Chunk<L>::kVec, OW = Chunk<L>::kOutWords, kChunks = kMaxVec / CV;
+  __shared__ uint32_t warp_max[32];
+  __shared__ float warp_fmax[32];
   __shared__ float s_inv;
+  __shared__ uint32_t s_bits;
 
   const int row = blockIdx.x, t = threadIdx.x, T = blockDim.x;
   const bool live = row < m;
   const uint16_t* xr = x + static_cast<int64_t>(row) * sx;
 
-  uint4 v[kMaxVec];
-  float amax = 0.f;
+  uint4 v[kChunks][CV];
+  uint32_t imax = 0;                                   // packed 16-bit max of |x| bit patterns
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int idx = t + i * T;
-    uint4 w = make_uint4(0u, 0u, 0u, 0u);
-    if (live && idx < nvec) {
-      if constexpr (VEC) {
-        w = __ldg(reinterpret_cast<const uint4*>(xr) + idx);
-      } else {
-        uint32_t e[8];
+  for (int i = 0; i < kChunks; ++i) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int col = idx * 8 + j;
-          e[j] = col < k ? static_cast<uint32_t>(__ldg(xr + col)) : 0u;
+    for (int c = 0; c < CV; ++c) {
+      const int idx = (t + i * T) * CV + c;
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      if (live && idx < nvec) {
+        if constexpr (VEC) {
+          w = __ldg(reinterpret_cast<const uint4*>(xr) + idx);
+        } else {
+          uint32_t e[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int col = idx * 8 + j;
+            e[j] = col < k ? static_cast<uint32_t>(__ldg(xr + col)) : 0u;
+          }
+          w = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
         }
-        w = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16),
-                       e[6] | (e[7] << 16));
       }
+      v[i][c] = w;
+      imax = __vmaxu2(imax, __vmaxu2(__vmaxu2(w.x & 0x7fff7fffu, w.y & 0x7fff7fffu),
+                                     __vmaxu2(w.z & 0x7fff7fffu, w.w & 0x7fff7fffu)));
     }
-    v[i] = w;
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(w.x)), fabsf(bf_hi(w.x))),
-                             fmaxf(fabsf(bf_lo(w.y)), fabsf(bf_hi(w.y)))));
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(bf_lo(w.z)), fabsf(bf_hi(w.z))),
-                             fmaxf(fabsf(bf_lo(w.w)), fabsf(bf_hi(w.w)))));
   }
 #pragma unroll
-  for (int d = 16; d; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-  if ((t & 31) == 0) warp_max[t >> 5] = amax;
+  for (int d = 16; d; d >>= 1) imax = __vmaxu2(imax, __shfl_xor_sync(0xffffffffu, imax, d));
+  if ((t & 31) == 0) warp_max[t >> 5] = imax;
   __syncthreads();
   if (t < 32) {
-    float a = t < (T >> 5) ? warp_max[t] : 0.f;
+    uint32_t a = t < (T >> 5) ? warp_max[t] : 0u;
+#pragma unroll
+    for (int d = 16; d; d >>= 1) a = __vmaxu2(a, __shfl_xor_sync(0xffffffffu, a, d));
+    if (t == 0) s_bits = max(a & 0xffffu, a >> 16);
+  }
+  __syncthreads();
+  const uint32_t bits = s_bits;
+  const bool special = bits >= 0x7f80u;                // the row holds Inf or NaN
+
+  float amax = __uint_as_float(bits << 16);
+  if (special) {
+    // absolute maximum with fmaxf semantics: NaN operands are ignored, Inf wins
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+      for (int c = 0; c < CV; ++c) {
+        const uint4 w = v[i][c];
+        a = fmaxf(a, fmaxf(fmaxf(fabsf(bf_lo(w.x)), fabsf(bf_hi(w.x))), fmaxf(fabsf(bf_lo(w.y)), fabsf(bf_hi(w.y)))));
+        a = fmaxf(a, fmaxf(fmaxf(fabsf(bf_lo(w.z)), fabsf(bf_hi(w.z))), fmaxf(fabsf(bf_lo(w.w)), fabsf(bf_hi(w.w)))));
+      }
 #pragma unroll
     for (int d = 16; d; d >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, d));
-    if (t == 0) {
-      const float scale = fmaxf(__fdiv_rn(fmaxf(a, 1e-12f), 127.f), 1.f / (127.f * 512.f));
-      s_inv = __fdiv_rn(1.f, scale);
-      sa[row] = live ? scale : 1.f;
-    }
+    if ((t & 31) == 0) warp_fmax[t >> 5] = a;
+    __syncthreads();
+    a = 0.f;
+    for (int i = 0; i < (T >> 5); ++i) a = fmaxf(a, warp_fmax[i]);
+    amax = a;
+  }
+  if (t == 0) {
+    const float scale = fmaxf(__fdiv_rn(fmaxf(amax, 1e-12f), 127.f), 1.f / (127.f * 512.f));
+    s_inv = __fdiv_rn(1.f, scale);
+    sa[row] = live ? scale : 1.f;
   }
   __syncthreads();
   const float inv = s_inv;
 
-  int8_t* qr = q + static_cast<int64_t>(row) * pk;
-  if constexpr (L == 4) {
-    // lifted row == quantised row, zero-padded to pk
-    const int nout = pk >> 3;
+  uint4* qr = reinterpret_cast<uint4*>(q + static_cast<int64_t>(row) * pk);
+  const int out_vecs = pk >> 4;
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int idx = t + i * T;
-      if (idx < nout) {
-        uint2 o = make_uint2(quant_pair_lo(v[i].x, v[i].y, inv), quant_pair_lo(v[i].z, v[i].w, inv));
-        if (!live) o = make_uint2(0u, 0u);
-        reinterpret_cast<uint2*>(qr)[idx] = o;
+  for (int i = 0; i < kChunks; ++i) {
+    const int chunk = t + i * T;
+    uint32_t qw[CV * 2 + 1], ow[OW];
+#pragma unroll
+    for (int c = 0; c < CV; ++c) {
+      const uint4 w = v[i][c];
+      if (special) {
+        qw[2 * c] = quant4_exact(w.x, w.y, inv);
+        qw[2 * c + 1] = quant4_exact(w.z, w.w, inv);
+      } else {
+        qw[2 * c] = quant4_fast(w.x, w.y, inv);
+        qw[2 * c + 1] = quant4_fast(w.z, w.w, inv);
       }
     }
-  } else {
-    constexpr int W = L / 2 - 1;
+    qw[CV * 2] = 0u;
+    lift_chunk<L>(qw, ow);
 #pragma unroll
-    for (int i = 0; i < kMaxVec; ++i) {
-      const int idx = t + i * T;
-      if (idx < nvec) {
-        uint2 o = make_uint2(quant_pair_lo(v[i].x, v[i].y, inv), quant_pair_lo(v[i].z, v[i].w, inv));
-        if (!live) o = make_uint2(0u, 0u);
-        reinterpret_cast<uint2*>(qs)[idx] = o;
-      }
-    }
-    if (t < 4) reinterpret_cast<uint32_t*>(qs + nvec * 8)[t] = 0u;   // tail-group lanes >= k
-    __syncthreads();
-    const int valid_words = (k + L - 1) / L * W;
-    const int nout = pk >> 4;
-    for (int ov = t; ov < nout; ov += T) {
-      uint32_t word[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int w = ov * 4 + j;
-        uint32_t value = 0u;
-        if (w < valid_words) {
-          const int src = (w / W) * L + 2 * (w % W);      // even byte offset
-          const uint16_t* p = reinterpret_cast<const uint16_t*>(qs + src);
-          value = static_cast<uint32_t>(p[0]) | (static_cast<uint32_t>(p[1]) << 16);
-        }
-        word[j] = value;
-      }
-      reinterpret_cast<uint4*>(qr)[ov] = make_uint4(word[0], word[1], word[2], word[3]);
+    for (int s = 0; s < OW / 4; ++s) {
+      const int ov = chunk * (OW / 4) + s;
+      if (ov < out_vecs) qr[ov] = make_uint4(ow[4 * s], ow[4 * s + 1], ow[4 * s + 2], ow[4 * s + 3]);
     }
   }
 }
@@ -136,24 +174,16 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
 template <int L, bool VEC>
 int launch_one(const void* x, int64_t sx, int m, int k, int pm, int pk, int8_t* q, float* sa,
                cudaStream_t stream) {
+  constexpr int CV = Chunk<L>::kVec, OW = Chunk<L>::kOutWords, kChunks = kMaxVec / CV;
   const int nvec = (k + 7) / 8;
-  const int need = L == 4 ? (pk >> 3) : nvec;       // vectors the register loop must cover
+  const int chunks_in = (nvec + CV - 1) / CV;
+  const int chunks_out = ((pk >> 2) + OW - 1) / OW;     // padding words are written too
+  const int chunks = chunks_in > chunks_out ? chunks_in : chunks_out;
   int threads = 32;
-  while (threads * kMaxVec < need) threads <<= 1;
+  while (threads * kChunks < chunks) threads <<= 1;
   SS_REQUIRE(threads <= kMaxThreads, SS_E_LIMIT, "front-end: K=%d beyond the supported %d", k,
              kMaxThreads * kMaxVec * 8);
-  const size_t smem = L == 4 ? 0 : static_cast<size_t>(nvec) * 8 + 16;
-  auto kernel = quant_lift_kernel<L, VEC>;
-  if (smem > 48 * 1024) {
-    static thread_local int configured_device = -1;
-    int dev = 0;
-    SS_CUDA(cudaGetDevice(&dev));
-    if (configured_device != dev) {
-      SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024));
-      configured_device = dev;
-    }
-  }
-  kernel<<<pm, threads, smem, stream>>>(static_cast<const uint16_t*>(x), sx, q, sa, m, k, pk, nvec);
+  quant_lift_kernel<L, VEC><<<pm, threads, 0, stream>>>(static_cast<const uint16_t*>(x), sx, q, sa, m, k, pk, nvec);
   SS_CUDA(cudaGetLastError());
   return SS_OK;
 }

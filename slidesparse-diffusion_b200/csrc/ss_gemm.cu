@@ -344,7 +344,7 @@ int encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* bas
   return SS_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][2][2] = {}; };
+struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][4] = {}; };
 DeviceInfo* device_info() {
   static std::mutex mu;
   static std::unordered_map<int, DeviceInfo> table;
@@ -380,6 +380,35 @@ int pick_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
     const double main = num_kb * feed[i] * nt / 256.0;
     const double tile_time = overlapped ? (main > epilogue ? main : epilogue) + 0.5 : main + epilogue + 0.5;
     const double cost = waves * tile_time;
+    if (best == 0 || cost < best) { best = cost; best_nt = nt; }
+  }
+  return best_nt;
+}
+
+// Token tile of the CTA-pair kernel (256 channels x NT tokens per pair).  Cost model in cycles,
+// fitted to measurements: a block of 128 lifted columns costs the shared-memory time of its two
+// MMAs (TMA writes plus operand reads of 2*(5 KB + 32*NT bytes) per MMA at 128 B/clk) plus a
+// fixed issue overhead; the epilogue (~32 cycles per token column) is hidden behind the next
+// tile's main loop when the accumulator is double buffered (NT <= 224) and exposed otherwise.
+int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
+  if (const char* env = std::getenv("SS_TOKEN_TILE")) {
+    const int v = std::atoi(env);
+    if (v == 128 || v == 192 || v == 224 || v == 256) return v;
+  }
+  const int64_t tiles_ch2 = (pn + 2 * kTileCh - 1) / (2 * kTileCh);
+  const double num_kb = static_cast<double>(pk / kBlockK);
+  const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
+  const int cand[4] = {224, 256, 192, 128};
+  double best = 0;
+  int best_nt = 224;
+  for (int i = 0; i < 4; ++i) {
+    const int nt = cand[i];
+    const int64_t tiles = tiles_ch2 * ((m + nt - 1) / nt);
+    const int64_t rounds = (tiles + pairs - 1) / pairs;
+    const double main = num_kb * (2.0 * (2.0 * (5120.0 + 32.0 * nt)) / 128.0 + 150.0);
+    const double epilogue = 32.0 * nt;
+    const double tile_time = nt <= 224 ? (main > epilogue ? main : epilogue) + 600.0 : main + epilogue + 600.0;
+    const double cost = static_cast<double>(rounds) * tile_time;
     if (best == 0 || cost < best) { best = cost; best_nt = nt; }
   }
   return best_nt;
@@ -443,15 +472,15 @@ int launch_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t st
 }
 
 // ---- CTA-pair launcher -----------------------------------------------------------------------
-template <int NT, int KB, bool I32, bool ADD>
+template <int NT, int KB, int MODE>
 int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
   using T = PairTile<NT, KB>;
-  auto kernel = sparse_gemm_pair_kernel<NT, KB, I32, ADD>;
-  if (!dev->pair_configured[cfg_index][I32][ADD]) {
+  auto kernel = sparse_gemm_pair_kernel<NT, KB, MODE>;
+  if (!dev->pair_configured[cfg_index][MODE]) {
     SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
-    dev->pair_configured[cfg_index][I32][ADD] = true;
+    dev->pair_configured[cfg_index][MODE] = true;
   }
-  CUtensorMap map_a, map_b, map_e;
+  CUtensorMap map_a, map_b, map_e, map_out;
   {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.pk / 2), static_cast<cuuint64_t>(a.pn)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.pk / 2)};
@@ -489,16 +518,30 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   const int64_t tiles = static_cast<int64_t>((k.tiles_ch + 1) / 2) * k.tiles_tok;
   const int64_t pairs = dev->sms / 2;
   const unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);
-  kernel<<<grid, kThreads, T::kSmemBytes, stream>>>(map_a, map_b, map_e, k);
+  if constexpr (MODE == kOutBf16Tma) {
+    // out[m, n] BF16, row pitch out_stride: one 32-channel x 32-token box per epilogue warp and chunk
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.out_stride) * 2};
+    const cuuint32_t box[2] = {32, 32};
+    int rc = encode(&map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  } else {
+    map_out = map_a;       // unused by the direct-store epilogues
+  }
+  kernel<<<grid, kThreads, T::kSmemBytes, stream>>>(map_a, map_b, map_e, map_out, k);
   SS_CUDA(cudaGetLastError());
   return SS_OK;
 }
 
 template <int NT, int KB>
 int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
-  if (a.int32_out) return launch_pair_t<NT, KB, true, false>(a, dev, cfg_index, stream);
-  if (a.addend) return launch_pair_t<NT, KB, false, true>(a, dev, cfg_index, stream);
-  return launch_pair_t<NT, KB, false, false>(a, dev, cfg_index, stream);
+  if (a.int32_out) return launch_pair_t<NT, KB, kOutInt32>(a, dev, cfg_index, stream);
+  if (a.addend) return launch_pair_t<NT, KB, kOutBf16Addend>(a, dev, cfg_index, stream);
+  // TMA stores need a 16-byte aligned base and row pitch
+  const bool tma_ok = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 && a.out_stride % 8 == 0;
+  const char* env = std::getenv("SS_TMA_STORE");
+  if (tma_ok && !(env && std::atoi(env) == 0)) return launch_pair_t<NT, KB, kOutBf16Tma>(a, dev, cfg_index, stream);
+  return launch_pair_t<NT, KB, kOutBf16>(a, dev, cfg_index, stream);
 }
 
 // Blocks of 128 lifted columns per pipeline stage: 2 wherever at least 3 stages still fit.
@@ -533,15 +576,15 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (int rc = check_args(a)) return rc;
   DeviceInfo* dev = device_info();
   SS_REQUIRE(dev, SS_E_CUDA, "gemm: no current CUDA device");
-  if (const char* env = std::getenv("SS_PAIR")) {
-    if (std::atoi(env) == 1) {
-      const char* t = std::getenv("SS_TOKEN_TILE");
-      switch (t ? std::atoi(t) : 256) {
-        case 128: return launch_pair_nt<128, 2>(a, dev, 0, stream);
-        case 192: return launch_pair_nt<192, 2>(a, dev, 1, stream);
-        case 224: return launch_pair_nt<224, 2>(a, dev, 2, stream);
-        default:  return launch_pair_nt<256, 2>(a, dev, 3, stream);
-      }
+  // The CTA-pair kernel is the default; SS_PAIR=0 selects the single-CTA kernel (kept for
+  // comparison and for token tiles of 64).
+  const char* pair_env = std::getenv("SS_PAIR");
+  if (!pair_env || std::atoi(pair_env) != 0) {
+    switch (pick_pair_token_tile(a.m, a.pn, a.pk, dev->sms)) {
+      case 128: return launch_pair_nt<128, 2>(a, dev, 0, stream);
+      case 192: return launch_pair_nt<192, 2>(a, dev, 1, stream);
+      case 224: return launch_pair_nt<224, 2>(a, dev, 2, stream);
+      default:  return launch_pair_nt<256, 2>(a, dev, 3, stream);
     }
   }
   const int nt = pick_token_tile(a.m, a.pn, a.pk, dev->sms);
@@ -568,9 +611,31 @@ static int resources_t(GemmResources* r) {
   return SS_OK;
 }
 
+template <int NT, int KB>
+static int pair_resources_t(GemmResources* r) {
+  using T = PairTile<NT, KB>;
+  auto kernel = sparse_gemm_pair_kernel<NT, KB, kOutBf16Tma>;
+  cudaFuncAttributes attr;
+  SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
+  SS_CUDA(cudaFuncGetAttributes(&attr, kernel));
+  r->threads = kThreads; r->smem = T::kSmemBytes; r->regs = attr.numRegs;
+  r->local = static_cast<int>(attr.localSizeBytes); r->ctas_per_sm = 1;
+  r->token_tile = NT; r->stages = T::kStages; r->tmem_cols = kTmemCols;
+  return SS_OK;
+}
+
 int gemm_resources(int64_t m, int64_t n, int64_t pk, GemmResources* r) {
   DeviceInfo* dev = device_info();
   SS_REQUIRE(dev, SS_E_CUDA, "gemm: no current CUDA device");
+  const char* pair_env = std::getenv("SS_PAIR");
+  if (!pair_env || std::atoi(pair_env) != 0) {
+    switch (pick_pair_token_tile(m, ceil_to(n, 32), pk, dev->sms)) {
+      case 128: return pair_resources_t<128, 2>(r);
+      case 192: return pair_resources_t<192, 2>(r);
+      case 224: return pair_resources_t<224, 2>(r);
+      default:  return pair_resources_t<256, 2>(r);
+    }
+  }
   const int nt = pick_token_tile(m, ceil_to(n, 32), pk, dev->sms);
   switch (nt) {
     case 256: return stage_blocks(nt) == 2 ? resources_t<256, 2>(r) : resources_t<256, 1>(r);

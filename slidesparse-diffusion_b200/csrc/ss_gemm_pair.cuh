@@ -38,7 +38,11 @@ struct PairTile {
   static constexpr int kOffB = kOffA + kStages * kABytes;
   static constexpr int kOffE = kOffB + kStages * kBBytes;
   static constexpr int kOffSa = kOffE + kStages * kEBytes;
-  static constexpr int kOffBar = kOffSa + 4 * NT * 4;
+  static constexpr int kOffStore = kOffSa + 4 * NT * 4;             // BF16 staging for TMA stores
+  static constexpr int kStoreTile = 32 * 32 * 2;                    // 32 tokens x 32 channels
+  static constexpr int kStoreBufs =
+      kOffStore + 2 * 4 * kStoreTile + 256 + 1024 <= 227 * 1024 ? 2 : 1;   // per epilogue warp
+  static constexpr int kOffBar = kOffStore + kStoreBufs * 4 * kStoreTile;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   static_assert(kStages >= 2, "pipeline depth");
   static_assert(kMetaCol + kStages * kMetaColsPerStage <= kTmemCols, "TMEM budget");
@@ -47,12 +51,22 @@ struct PairTile {
   static_assert(kBBlock % 1024 == 0, "B blocks must keep the 128B-swizzle alignment");
 };
 
-template <int NT, int KB, bool INT32_OUT, bool HAS_ADDEND>
+// Output modes of the epilogue.
+enum : int {
+  kOutBf16 = 0,        // BF16, direct stores (any n, any alignment)
+  kOutInt32 = 1,       // raw INT32 accumulators, direct stores
+  kOutBf16Addend = 2,  // BF16 with an addend, direct stores
+  kOutBf16Tma = 3,     // BF16 staged in shared memory and written with TMA tiled stores
+};
+
+template <int NT, int KB, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b,
-                        const __grid_constant__ CUtensorMap map_e, const KernelArgs args) {
+                        const __grid_constant__ CUtensorMap map_e,
+                        const __grid_constant__ CUtensorMap map_out, const KernelArgs args) {
   using T = PairTile<NT, KB>;
+  constexpr bool INT32_OUT = MODE == kOutInt32, HAS_ADDEND = MODE == kOutBf16Addend;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -82,6 +96,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
     ptx::prefetch_tensormap(&map_e);
+    if constexpr (MODE == kOutBf16Tma) ptx::prefetch_tensormap(&map_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -164,7 +179,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int quad = warp & 3;
     float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
-    uint32_t acc_it = 0;
+    uint32_t acc_it = 0, store_it = 0;
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
@@ -193,17 +208,55 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       };
       uint32_t r0[32], r1[32];
       ptx::tc_ld_32x32b_x32(t_addr, r0);
+      auto emit = [&](const uint32_t (&r)[32], int c) {
+        if constexpr (MODE == kOutBf16Tma) {
+          // lane = channel: write the 32x32 BF16 tile token-major, then one tiled store per warp
+          uint8_t* stage = smem + T::kOffStore + ((warp - 2) * T::kStoreBufs + (store_it % T::kStoreBufs)) * T::kStoreTile;
+          if (lane == 0) {
+            if constexpr (T::kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
+          }
+          __syncwarp();
+          const float* sa_c = sa_s + c * 32;
+          __nv_bfloat16* tile_out = reinterpret_cast<__nv_bfloat16*>(stage) + lane;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 s4 = reinterpret_cast<const float4*>(sa_c)[j4];
+            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const int j = j4 * 4 + jj;
+              const float y = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[j])), __fmul_rn(sv[jj], sw), bias);
+              tile_out[j * 32] = __float2bfloat16_rn(y);
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
+            // beyond the last channel is not issued at all
+            if (ch < args.n) ptx::tma_store_2d(&map_out, stage, ch, tok0 + c * 32);
+            ptx::bulk_commit();
+          }
+          ++store_it;
+        } else {
+          store_chunk<INT32_OUT, HAS_ADDEND>(r, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
+        }
+      };
 #pragma unroll 1
       for (int c = 0; c < chunks; c += 2) {
         ptx::tc_wait_ld();
         if (c + 1 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 1) * 32, r1); else release();
-        store_chunk<INT32_OUT, HAS_ADDEND>(r0, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
+        emit(r0, c);
         if (c + 1 < chunks) {
           ptx::tc_wait_ld();
           if (c + 2 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 2) * 32, r0); else release();
-          store_chunk<INT32_OUT, HAS_ADDEND>(r1, args, sa_s + (c + 1) * 32, tok0 + (c + 1) * 32, ch, ch_ok, sw, bias);
+          emit(r1, c + 1);
         }
       }
+    }
+    if constexpr (MODE == kOutBf16Tma) {
+      if (lane == 0) ptx::bulk_wait_all();
+      __syncwarp();
     }
     if (!ok && lane == 0) atomicOr(args.status, kStatusEpilogueTimeout);
   }

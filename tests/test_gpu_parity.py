@@ -67,10 +67,16 @@ def test_gemm_int32_accumulators_bit_exact(backend, oracle, mode, m, k, n):
     assert np.array_equal(acc.cpu().numpy(), case["acc"])
 
 
-@pytest.mark.parametrize("tile", ["64", "128", "192", "256"])
-def test_every_token_tile_is_exact(backend, oracle, monkeypatch, tile):
+@pytest.mark.parametrize("pair,tile", [("1", "128"), ("1", "192"), ("1", "224"), ("1", "256"),
+                                       ("0", "64"), ("0", "128"), ("0", "192"), ("0", "256")])
+def test_every_kernel_variant_is_exact(backend, oracle, oracle_c, monkeypatch, pair, tile):
+    """CTA-pair kernel (default) and single-CTA kernel, every token tile, ragged edges in M, N, K."""
+    monkeypatch.setenv("SS_PAIR", pair)
     monkeypatch.setenv("SS_TOKEN_TILE", tile)
     case = prepare_case(oracle, 700, 640, 300, 6, seed=int(tile))
+    out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
+                     dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), 700, 300)
+    assert np.array_equal(bits(out), oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"]))
     q, packed, meta = dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32)
     acc = c_gemm_int32(backend, q, packed, meta, 700, 300)
     assert np.array_equal(acc.cpu().numpy(), case["acc"])
