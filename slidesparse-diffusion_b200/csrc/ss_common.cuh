@@ -273,6 +273,11 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t mask) {
 __device__ __forceinline__ void tc_cp_128x128b_pair(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
+// 128 lanes x 256 bit: two 16-byte column blocks of the source (leading-dimension offset apart)
+// land in 8 consecutive TMEM columns.
+__device__ __forceinline__ void tc_cp_128x256b_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 __device__ __forceinline__ void tc_mma_sp_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                                   uint32_t e_tmem, uint32_t idesc, uint32_t accumulate) {
   asm volatile(

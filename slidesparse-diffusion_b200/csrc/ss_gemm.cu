@@ -77,6 +77,7 @@ struct KernelArgs {
   int m, n;
   int tiles_ch, tiles_tok, num_kb;
   uint32_t* status;
+  int wide_cp;          // CTA-pair kernel: copy a stage's two metadata blocks with one tcgen05.cp
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes,
@@ -344,7 +345,7 @@ int encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* bas
   return SS_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][4] = {}; };
+struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][5] = {}; };
 DeviceInfo* device_info() {
   static std::mutex mu;
   static std::unordered_map<int, DeviceInfo> table;
@@ -456,6 +457,7 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   k.tiles_tok = static_cast<int>((a.m + NT - 1) / NT);
   k.num_kb = static_cast<int>(a.pk / kBlockK);
   k.status = device_status_ptr();
+  k.wide_cp = 0;
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
   const int64_t tiles = static_cast<int64_t>(k.tiles_ch) * k.tiles_tok;
   const unsigned grid = static_cast<unsigned>(tiles < dev->sms ? tiles : dev->sms);
@@ -515,6 +517,7 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   k.num_kb = static_cast<int>(a.pk / kBlockK);
   k.status = device_status_ptr();
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
+  { const char* env = std::getenv("SS_WIDE_CP"); k.wide_cp = env ? std::atoi(env) : 1; }
   const int64_t tiles = static_cast<int64_t>((k.tiles_ch + 1) / 2) * k.tiles_tok;
   const int64_t pairs = dev->sms / 2;
   const unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);
@@ -528,7 +531,7 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   } else {
     map_out = map_a;       // unused by the direct-store epilogues
   }
-  kernel<<<grid, kThreads, T::kSmemBytes, stream>>>(map_a, map_b, map_e, map_out, k);
+  kernel<<<grid, kPairThreads, T::kSmemBytes, stream>>>(map_a, map_b, map_e, map_out, k);
   SS_CUDA(cudaGetLastError());
   return SS_OK;
 }
@@ -539,8 +542,10 @@ int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream
   if (a.addend) return launch_pair_t<NT, KB, kOutBf16Addend>(a, dev, cfg_index, stream);
   // TMA stores need a 16-byte aligned base and row pitch
   const bool tma_ok = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 && a.out_stride % 8 == 0;
-  const char* env = std::getenv("SS_TMA_STORE");
-  if (tma_ok && !(env && std::atoi(env) == 0)) return launch_pair_t<NT, KB, kOutBf16Tma>(a, dev, cfg_index, stream);
+  const char* env = std::getenv("SS_STORE");          // 0 direct, 1 TMA, 2 staged 16-byte stores
+  const int store = env ? std::atoi(env) : 2;
+  if (tma_ok && store == 1) return launch_pair_t<NT, KB, kOutBf16Tma>(a, dev, cfg_index, stream);
+  if (tma_ok && store == 2) return launch_pair_t<NT, KB, kOutBf16Staged>(a, dev, cfg_index, stream);
   return launch_pair_t<NT, KB, kOutBf16>(a, dev, cfg_index, stream);
 }
 
@@ -618,7 +623,7 @@ static int pair_resources_t(GemmResources* r) {
   cudaFuncAttributes attr;
   SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
   SS_CUDA(cudaFuncGetAttributes(&attr, kernel));
-  r->threads = kThreads; r->smem = T::kSmemBytes; r->regs = attr.numRegs;
+  r->threads = kPairThreads; r->smem = T::kSmemBytes; r->regs = attr.numRegs;
   r->local = static_cast<int>(attr.localSizeBytes); r->ctas_per_sm = 1;
   r->token_tile = NT; r->stages = T::kStages; r->tmem_cols = kTmemCols;
   return SS_OK;

@@ -20,6 +20,9 @@
 //                8 epilogue warps of the pair (rank 1 arrives through shared::cluster).
 #pragma once
 
+constexpr int kPairEpiWarps = 8;                       // two warps per TMEM lane quadrant
+constexpr int kPairThreads = 64 + 32 * kPairEpiWarps;
+
 template <int NT, int KB>
 struct PairTile {
   static constexpr int kHalf = NT / 2;                             // B token rows held per CTA
@@ -29,7 +32,15 @@ struct PairTile {
   static constexpr int kEBlock = kTileCh * kBlockK / 8;
   static constexpr int kEBytes = kEBlock * KB;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;  // per CTA
-  static constexpr int kStagesRaw = (212 * 1024) / kStageBytes;
+  static constexpr int kSaBytes = kPairEpiWarps * NT * 4;           // token scales, one copy per warp
+  static constexpr int kStoreTile = 32 * 32 * 2;                    // 32 tokens x 32 channels BF16
+  static constexpr int kFixed = kSaBytes + 256 + 1024;              // + barrier block + alignment slack
+  static constexpr int kBudget = 227 * 1024 - kFixed;
+  // two staging tiles per epilogue warp if at least four pipeline stages still fit, else one
+  static constexpr int kStages2 = (kBudget - 2 * kPairEpiWarps * kStoreTile) / kStageBytes;
+  static constexpr int kStages1 = (kBudget - 1 * kPairEpiWarps * kStoreTile) / kStageBytes;
+  static constexpr int kStoreBufs = kStages2 >= 4 ? 2 : 1;
+  static constexpr int kStagesRaw = kStoreBufs == 2 ? kStages2 : kStages1;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kMetaColsPerStage = 4 * KB;
   static constexpr int kAccBufs = (kTmemCols - kStages * kMetaColsPerStage) / NT >= 2 ? 2 : 1;
@@ -38,11 +49,8 @@ struct PairTile {
   static constexpr int kOffB = kOffA + kStages * kABytes;
   static constexpr int kOffE = kOffB + kStages * kBBytes;
   static constexpr int kOffSa = kOffE + kStages * kEBytes;
-  static constexpr int kOffStore = kOffSa + 4 * NT * 4;             // BF16 staging for TMA stores
-  static constexpr int kStoreTile = 32 * 32 * 2;                    // 32 tokens x 32 channels
-  static constexpr int kStoreBufs =
-      kOffStore + 2 * 4 * kStoreTile + 256 + 1024 <= 227 * 1024 ? 2 : 1;   // per epilogue warp
-  static constexpr int kOffBar = kOffStore + kStoreBufs * 4 * kStoreTile;
+  static constexpr int kOffStore = kOffSa + kSaBytes;               // BF16 staging for TMA stores
+  static constexpr int kOffBar = kOffStore + kStoreBufs * kPairEpiWarps * kStoreTile;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   static_assert(kStages >= 2, "pipeline depth");
   static_assert(kMetaCol + kStages * kMetaColsPerStage <= kTmemCols, "TMEM budget");
@@ -57,10 +65,11 @@ enum : int {
   kOutInt32 = 1,       // raw INT32 accumulators, direct stores
   kOutBf16Addend = 2,  // BF16 with an addend, direct stores
   kOutBf16Tma = 3,     // BF16 staged in shared memory and written with TMA tiled stores
+  kOutBf16Staged = 4,  // BF16 transposed through shared memory, 16-byte global stores
 };
 
 template <int NT, int KB, int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_e,
@@ -90,7 +99,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int b = 0; b < T::kAccBufs; ++b) {
       ptx::mbar_init(&bar_acc_full[b], 1);
-      ptx::mbar_init(&bar_acc_empty[b], 8);
+      ptx::mbar_init(&bar_acc_empty[b], 2 * kPairEpiWarps);
     }
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_a);
@@ -143,6 +152,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       constexpr uint32_t a_layout = KB == 2 ? 2u : 4u, a_sbo = KB == 2 ? 1024u : 512u;
       uint32_t consumed = 0, acc_it = 0;
       bool ok = true, ready = false;
+      int release_stage = -1;        // stage whose MMAs are issued but whose barrier is not yet committed
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
         const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
         if (!ptx::mbar_wait(&bar_acc_empty[buf], (acc_use & 1u) ^ 1u)) { ok = false; break; }
@@ -158,8 +168,14 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t b_addr = ptx::smem_u32(smem + T::kOffB + s * T::kBBytes);
           const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
           const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
-          for (int h = 0; h < nkb; ++h)
-            ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+          if (KB == 2 && nkb == 2 && args.wide_cp) {
+            // both metadata blocks of the stage in one instruction: block h is the h-th 16-byte
+            // column of a 128 x 32-byte matrix whose columns lie kEBlock bytes apart
+            ptx::tc_cp_128x256b_pair(e_tmem, smem_desc(e_addr, T::kEBlock, 128, 0));
+          } else {
+            for (int h = 0; h < nkb; ++h)
+              ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+          }
           {
             const uint32_t s2 = (consumed + 1) % T::kStages, use2 = (consumed + 1) / T::kStages;
             ready = mbar_peek(&bar_full[s2], use2 & 1u);
@@ -168,8 +184,17 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             const uint64_t adesc = smem_desc(a_addr + j * 32, 16, a_sbo, a_layout);
             const uint64_t bdesc = smem_desc(b_addr + (j >> 1) * T::kBBlock + (j & 1) * 64, 16, 1024, 2);
             ptx::tc_mma_sp_i8_pair(d_tmem, adesc, bdesc, e_tmem + j * 2, idesc, (st | j) != 0 ? 1u : 0u);
+            if (j == 0 && release_stage >= 0) {
+              // the previous stage is handed back while this stage's first MMA keeps the pipe busy
+              ptx::tc_commit_pair(&bar_empty[release_stage], 3);
+              release_stage = -1;
+            }
           }
-          ptx::tc_commit_pair(&bar_empty[s], 3);
+          release_stage = static_cast<int>(s);
+        }
+        if (release_stage >= 0) {
+          ptx::tc_commit_pair(&bar_empty[release_stage], 3);
+          release_stage = -1;
         }
         if (ok) ptx::tc_commit_pair(&bar_acc_full[buf], 3);
       }
@@ -177,7 +202,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
-    const int quad = warp & 3;
+    const int quad = warp & 3;                    // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;             // the quadrant's two warps take alternate chunks
     float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
     uint32_t acc_it = 0, store_it = 0;
     bool ok = true;
@@ -207,13 +233,14 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) ptx::mbar_arrive_rank0(&bar_acc_empty[buf]);
       };
       uint32_t r0[32], r1[32];
-      ptx::tc_ld_32x32b_x32(t_addr, r0);
       auto emit = [&](const uint32_t (&r)[32], int c) {
-        if constexpr (MODE == kOutBf16Tma) {
+        if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16Staged) {
           // lane = channel: write the 32x32 BF16 tile token-major, then one tiled store per warp
           uint8_t* stage = smem + T::kOffStore + ((warp - 2) * T::kStoreBufs + (store_it % T::kStoreBufs)) * T::kStoreTile;
-          if (lane == 0) {
-            if constexpr (T::kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
+          if constexpr (MODE == kOutBf16Tma) {
+            if (lane == 0) {
+              if constexpr (T::kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
+            }
           }
           __syncwarp();
           const float* sa_c = sa_s + c * 32;
@@ -229,28 +256,57 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               tile_out[j * 32] = __float2bfloat16_rn(y);
             }
           }
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
-            // beyond the last channel is not issued at all
-            if (ch < args.n) ptx::tma_store_2d(&map_out, stage, ch, tok0 + c * 32);
-            ptx::bulk_commit();
+          if constexpr (MODE == kOutBf16Tma) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
+              // beyond the last channel is not issued at all
+              if (ch < args.n) ptx::tma_store_2d(&map_out, stage, ch, tok0 + c * 32);
+              ptx::bulk_commit();
+            }
+          } else {
+            // read the tile back token-major: four lanes cover the 64 bytes (32 channels) of a token
+            __syncwarp();
+            const int ch_base = ch - lane + (lane & 3) * 8;
+            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int row = (lane >> 2) + 8 * i, tok = tok0 + c * 32 + row;
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 64 + (lane & 3) * 16);
+              if (tok < args.m) {
+                __nv_bfloat16* dst = out + static_cast<long long>(tok) * args.out_stride + ch_base;
+                if (ch_base + 8 <= args.n) {
+                  *reinterpret_cast<uint4*>(dst) = v;
+                } else {
+                  const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+                  for (int t = 0; t < 8; ++t)
+                    if (ch_base + t < args.n) dst[t] = e[t];
+                }
+              }
+            }
           }
           ++store_it;
         } else {
           store_chunk<INT32_OUT, HAS_ADDEND>(r, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
         }
       };
+      const int mine = chunks > half ? (chunks - half + 1) / 2 : 0;      // chunks half, half+2, ...
+      if (mine == 0) {
+        release();
+      } else {
+        ptx::tc_ld_32x32b_x32(t_addr + half * 32, r0);
 #pragma unroll 1
-      for (int c = 0; c < chunks; c += 2) {
-        ptx::tc_wait_ld();
-        if (c + 1 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 1) * 32, r1); else release();
-        emit(r0, c);
-        if (c + 1 < chunks) {
+        for (int i = 0; i < mine; i += 2) {
+          const int c = half + 2 * i;
           ptx::tc_wait_ld();
-          if (c + 2 < chunks) ptx::tc_ld_32x32b_x32(t_addr + (c + 2) * 32, r0); else release();
-          emit(r1, c + 1);
+          if (i + 1 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + 2) * 32, r1); else release();
+          emit(r0, c);
+          if (i + 1 < mine) {
+            ptx::tc_wait_ld();
+            if (i + 2 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + 4) * 32, r0); else release();
+            emit(r1, c + 2);
+          }
         }
       }
     }
