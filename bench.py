@@ -39,6 +39,9 @@ MODES = (6, 8)
 SHAPES = ((3072, 9216), (3072, 12288), (12288, 3072))      # (K, N)
 TOKENS = (256, 1024, 1536, 4096, 16384)
 SAMPLE_TOKENS = 48            # rows per projection in the CPU sample (M = 1536 case)
+# dram__bytes_read+write per GEMM launch from the committed ncu capture (profiles/), averaged over
+# the 30 launches of a step by algorithmic-byte share; None until a capture of this kernel exists
+TRAFFIC_BYTES_PER_LAUNCH = None
 
 
 def logical_ops(tokens=TOKENS):
@@ -300,6 +303,8 @@ def main():
     pk = peaks()
     sparse_peak = 4.0 * pk["bf16_tflops"]
     gemm_tops = step_ops / (gemm_ms * 1e-3) / 1e12
+    executed_ops = sum(2 * (-(-m // 32) * 32) * (-(-n // 32) * 32) * pk_of[(mode, k)] for (mode, k, n, m) in calls)
+    executed_tops = executed_ops / (gemm_ms * 1e-3) / 1e12
     front_bytes = sum(2 * m * k + (-(-m // 32) * 32) * (pk_of[(mode, k)] + 4) for (mode, m, k) in quantised)
     front_gbs = front_bytes / (front_ms * 1e-3) / 1e9
 
@@ -345,6 +350,26 @@ def main():
                "sample": f"6 projections (4:6+6:8 x 3 FLUX shapes) at M=1536 restricted to {SAMPLE_TOKENS} "
                          f"token rows, repeated for {total_s:.1f} s"}
 
+    tp = None
+    if world > 1:
+        from slidesparse_diffusion_b200 import sharding
+        tp_m, tp_k, tp_n, tp_mode = 1536, 3072, 12288, 6
+        qweight, scales = oracle.make_weight(tp_n, tp_k, tp_mode, seed=77)
+        shard, _ = sharding.prepare_shard(torch.from_numpy(qweight), torch.from_numpy(scales), None, tp_mode, rank, world)
+        tp_op = sharding.TensorParallelProjection(shard.to(device), sharding.shard_columns(tp_n, world))
+        tp_x = dev_x[(tp_m, tp_k)]
+        for _ in range(3):
+            tp_op(tp_x)
+        barrier()
+        begin.record()
+        for _ in range(10):
+            tp_op(tp_x)
+        end.record()
+        barrier()
+        t = torch.tensor([begin.elapsed_time(end) / 10], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        tp = {"shape_mkn": [tp_m, tp_k, tp_n], "mode": "4:6", "ms": float(t.item()),
+              "what": "N-split shards + NCCL all-gather of BF16 outputs, eager launches"}
     if rank == 0:
         line = {
             "metric": "sparse_w8a8_linear_tops", "value": value, "unit": "TOPS", "n_gpus": world,
@@ -360,13 +385,16 @@ def main():
             "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": 2 * len(calls) * args.steps,
             "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": sparse_peak, "unit": "TFLOP/s",
-                         "frac": gemm_tops / sparse_peak, "traffic": None,
+                         "frac": gemm_tops / sparse_peak, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                         "executed_tops": executed_tops, "executed_frac": executed_tops / sparse_peak,
+                         "executed_frac_of_nominal_9000": executed_tops / 9000.0,
                          "kernel": "sparse_gemm_kernel (30 launches per step)",
                          "peak_source": f"4 x {pk['source']} dense bf16 {pk['bf16_tflops']} TFLOP/s "
                                         "(2:4-sparse INT8 proxy; nominal 9000)"},
             "roofline_frontend": {"bound": "hbm", "achieved": front_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
                                   "frac": front_gbs / pk["hbm_gbs"], "kernel": "quant_lift_kernel"},
             "cpu_baseline": cpu,
+            "tp_variant": tp,
         }
         print(json.dumps(line))
     if world > 1:

@@ -386,11 +386,12 @@ int pick_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   return best_nt;
 }
 
-// Token tile of the CTA-pair kernel (256 channels x NT tokens per pair).  Cost model in cycles,
-// fitted to measurements: a block of 128 lifted columns costs the shared-memory time of its two
-// MMAs (TMA writes plus operand reads of 2*(5 KB + 32*NT bytes) per MMA at 128 B/clk) plus a
-// fixed issue overhead; the epilogue (~32 cycles per token column) is hidden behind the next
-// tile's main loop when the accumulator is double buffered (NT <= 224) and exposed otherwise.
+// Token tile of the CTA-pair kernel (256 channels x NT tokens per pair).  Cost model in SM
+// cycles, fitted to CUDA-event timings on B200: a block of 128 lifted columns costs about 440
+// cycles for every double-buffered tile (the main loop is bound by the issue rate of the pair's
+// tcgen05 operations, not by N) and about 560 for NT = 256, whose accumulator cannot be double
+// buffered (its epilogue, ~3000 cycles, is exposed as well); a tile costs 1500 cycles on top and
+// never less than its epilogue (~38 cycles per token column).  Ties go to the smaller tile.
 int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   if (const char* env = std::getenv("SS_TOKEN_TILE")) {
     const int v = std::atoi(env);
@@ -399,18 +400,17 @@ int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   const int64_t tiles_ch2 = (pn + 2 * kTileCh - 1) / (2 * kTileCh);
   const double num_kb = static_cast<double>(pk / kBlockK);
   const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
-  const int cand[4] = {224, 256, 192, 128};
+  const int cand[4] = {128, 192, 224, 256};
   double best = 0;
   int best_nt = 224;
   for (int i = 0; i < 4; ++i) {
     const int nt = cand[i];
     const int64_t tiles = tiles_ch2 * ((m + nt - 1) / nt);
     const int64_t rounds = (tiles + pairs - 1) / pairs;
-    const double main = num_kb * (2.0 * (2.0 * (5120.0 + 32.0 * nt)) / 128.0 + 150.0);
-    const double epilogue = 32.0 * nt;
-    const double tile_time = nt <= 224 ? (main > epilogue ? main : epilogue) + 600.0 : main + epilogue + 600.0;
-    const double cost = static_cast<double>(rounds) * tile_time;
-    if (best == 0 || cost < best) { best = cost; best_nt = nt; }
+    const double main = num_kb * (nt == 256 ? 560.0 : 440.0) + 1500.0 + (nt == 256 ? 3000.0 : 0.0);
+    const double epilogue = 38.0 * nt;
+    const double cost = static_cast<double>(rounds) * (main > epilogue ? main : epilogue);
+    if (best == 0 || cost < best * 0.999) { best = cost; best_nt = nt; }
   }
   return best_nt;
 }
@@ -543,7 +543,7 @@ int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream
   // TMA stores need a 16-byte aligned base and row pitch
   const bool tma_ok = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 && a.out_stride % 8 == 0;
   const char* env = std::getenv("SS_STORE");          // 0 direct, 1 TMA, 2 staged 16-byte stores
-  const int store = env ? std::atoi(env) : 2;
+  const int store = env ? std::atoi(env) : 1;
   if (tma_ok && store == 1) return launch_pair_t<NT, KB, kOutBf16Tma>(a, dev, cfg_index, stream);
   if (tma_ok && store == 2) return launch_pair_t<NT, KB, kOutBf16Staged>(a, dev, cfg_index, stream);
   return launch_pair_t<NT, KB, kOutBf16>(a, dev, cfg_index, stream);

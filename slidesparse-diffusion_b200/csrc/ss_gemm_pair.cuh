@@ -207,6 +207,28 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
     uint32_t acc_it = 0, store_it = 0;
     bool ok = true;
+    // Scales of a tile are fetched one tile ahead into registers (the loads fly while the
+    // previous tile is processed) and parked in shared memory when the tile starts.
+    constexpr int kSaRegs = (NT + 31) / 32;
+    float sa_next[kSaRegs], sw_next = 1.f, bias_next = 0.f;
+    auto prefetch = [&](int t) {
+      const int pch = (t % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
+      const int ptok0 = (t / tiles_ch2) * NT;
+#pragma unroll
+      for (int i = 0; i < kSaRegs; ++i) {
+        const int tok = ptok0 + lane + 32 * i;
+        sa_next[i] = (lane + 32 * i < NT && tok < args.m) ? __ldg(args.sa + tok) : 1.f;
+      }
+      sw_next = 1.f;
+      bias_next = 0.f;
+      if (pch < args.n) {
+        sw_next = __ldg(args.sw + pch);
+        if (args.bias) bias_next = __ldg(args.bias + pch);
+      }
+    };
+    if constexpr (!INT32_OUT) {
+      if (pair < num_tiles) prefetch(pair);
+    }
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
       const int ch = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
@@ -215,12 +237,13 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       float sw = 1.f, bias = 0.f;
       if constexpr (!INT32_OUT) {
         __syncwarp();
-        for (int i = lane; i < NT; i += 32) sa_s[i] = tok0 + i < args.m ? __ldg(args.sa + tok0 + i) : 1.f;
-        if (ch_ok) {
-          sw = __ldg(args.sw + ch);
-          if (args.bias) bias = __ldg(args.bias + ch);
-        }
+#pragma unroll
+        for (int i = 0; i < kSaRegs; ++i)
+          if (lane + 32 * i < NT) sa_s[lane + 32 * i] = sa_next[i];
+        sw = sw_next;
+        bias = bias_next;
         __syncwarp();
+        if (tile + num_pairs < num_tiles) prefetch(tile + num_pairs);
       }
       int chunks = (args.m - tok0 + 31) / 32;
       chunks = chunks < NT / 32 ? chunks : NT / 32;

@@ -1,0 +1,86 @@
+"""Multi-GPU use of the projection: output-channel column shards, one process per GPU.
+
+The reference is single-GPU (it refuses anything else, `sdacc/diffusion_research/runner.py:13-18`).
+The projection shards naturally along output channels: rank g packs and keeps only rows
+[start_g, end_g) of the quantised weight (with the matching scales and bias), every rank
+quantises the full activation itself, and no data moves between GPUs.  Where a caller needs the
+full [M, N] output on every rank (tensor-parallel use inside a model) the shards are gathered
+with one NCCL all-gather over NVLink.
+"""
+import torch
+import torch.distributed as dist
+
+from .packing import group_size
+from .runtime import PackedLinear
+
+
+def shard_columns(n, world, members=None, align=32):
+    """[(start, end)] per rank: contiguous channel ranges with `align`-aligned starts that never
+    overlap and together cover [0, n).  Trailing ranks may be empty when n is small.  `members`
+    (widths of a fused projection such as Q|K|V) is only checked for consistency: a fused output
+    is split by widths after the gather, so member boundaries need not coincide with ranks."""
+    if world <= 0 or n <= 0:
+        raise ValueError("positive channel count and world size required")
+    if members is not None and sum(members) != n:
+        raise ValueError("member widths must add up to n")
+    units = -(-n // align)
+    base, extra = divmod(units, world)
+    bounds, start = [], 0
+    for rank in range(world):
+        width = (base + (1 if rank < extra else 0)) * align
+        end = min(n, start + width)
+        bounds.append((start, end))
+        start = end
+    return bounds
+
+
+def prepare_shard(qweight, scales, bias, mode, rank, world, members=None, **kwargs):
+    """PackedLinear for this rank's channel range of a full CPU int8 weight; also returns the range."""
+    n = qweight.shape[0]
+    start, end = shard_columns(n, world, members)[rank]
+    if end <= start:
+        raise ValueError(f"rank {rank} of {world} owns no channels of a {n}-channel projection")
+    shard_bias = None if bias is None or bias.numel() == 0 else bias[start:end]
+    op = PackedLinear.prepare(qweight[start:end].contiguous(), scales[start:end], shard_bias,
+                              group_size(mode), **kwargs)
+    return op, (start, end)
+
+
+def all_gather_columns(local, bounds, group=None):
+    """Gather [..., n_rank] shards into [..., n] on every rank (one all-gather; ragged shards are
+    padded to the widest one for the collective and trimmed afterwards)."""
+    world = dist.get_world_size(group)
+    if len(bounds) != world:
+        raise ValueError("one channel range per rank required")
+    widths = [end - start for start, end in bounds]
+    widest = max(widths)
+    lead = local.shape[:-1]
+    send = local
+    if local.shape[-1] != widest:
+        send = local.new_zeros((*lead, widest))
+        send[..., :local.shape[-1]] = local
+    send = send.contiguous()
+    if dist.get_backend(group) == "nccl":
+        gathered = local.new_empty((world, *lead, widest))
+        dist.all_gather_into_tensor(gathered, send, group=group)
+        parts = [gathered[r] for r in range(world)]
+    else:
+        parts = [torch.empty_like(send) for _ in range(world)]
+        dist.all_gather(parts, send, group=group)
+    return torch.cat([parts[r][..., :widths[r]] for r in range(world)], dim=-1)
+
+
+class TensorParallelProjection(torch.nn.Module):
+    """N-split tensor-parallel projection: local column shard + all-gather of the BF16 outputs."""
+
+    def __init__(self, shard, bounds, group=None):
+        super().__init__()
+        self.shard, self.bounds, self.group = shard, list(bounds), group
+        self.n = self.bounds[-1][1]
+
+    def forward(self, x, output_addend=None):
+        rank = dist.get_rank(self.group)
+        start, end = self.bounds[rank]
+        addend = None if output_addend is None else output_addend[..., start:end]
+        local = self.shard(x) if addend is None else self.shard(x, output_addend=addend)
+        return all_gather_columns(local, self.bounds, self.group)
