@@ -21,6 +21,11 @@ Printed JSON line (rank 0):
 pack restated in oracle/, with an int32 torch matmul) on a bounded sample of the same workload.
 With N > 1 (torchrun) every rank runs the sweep on its own weight shard (independent output
 channel shards, no collective); value = all ranks' operations / max-over-ranks time.
+
+`--workload dit-xl-512 | pixart-sigma-1024 | sd35-large-512` instead times one full denoise step
+(model forward on the CFG pair + guidance + sampler update, one CUDA graph) of a random-init
+transformer of that shape, with the routed projections sparse and with the same projections dense
+BF16 (dense measured before and after the sparse run); data-parallel over images when N > 1.
 """
 import argparse
 import json
@@ -39,9 +44,10 @@ MODES = (6, 8)
 SHAPES = ((3072, 9216), (3072, 12288), (12288, 3072))      # (K, N)
 TOKENS = (256, 1024, 1536, 4096, 16384)
 SAMPLE_TOKENS = 48            # rows per projection in the CPU sample (M = 1536 case)
-# dram__bytes_read+write per GEMM launch from the committed ncu capture (profiles/), averaged over
-# the 30 launches of a step by algorithmic-byte share; None until a capture of this kernel exists
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read+write of the GEMM kernel divided by its algorithmic bytes, from the committed ncu
+# capture of two M=4096 launches (profiles/sparse_gemm_pair_kernel_flux_M4096.md: 121.7/116.0 MB and
+# 140.0/123.9 MB); the bench scales the average algorithmic bytes per launch of its step by it
+TRAFFIC_OVER_ALGORITHMIC = (121.7 + 140.0) / (116.0 + 123.9)
 
 
 def logical_ops(tokens=TOKENS):
@@ -162,6 +168,89 @@ def run_reference(args, rank, world):
     }))
 
 
+def run_denoise(args, rank, world, local_rank):
+    """Denoise-step latency: sparse routed projections against dense BF16 on the same model."""
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    sdk = load_package()
+    sdk.load_native()
+    from slidesparse_diffusion_b200 import denoiser, backend
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    overrides = {} if args.blocks is None else {"blocks": args.blocks}
+    model = denoiser.build(args.workload, device=device, seed=rank, **overrides)
+    spec = model.spec
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(loop, steps, warmup):
+        """ms per denoise step over `steps` steps of the sampling loop (max over ranks)."""
+        loop.run(seed=rank, steps=max(warmup, 3))
+        barrier()
+        begin.record()
+        loop.run(seed=rank, steps=steps)
+        end.record()
+        barrier()
+        t = torch.tensor([begin.elapsed_time(end) / steps], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    steps = min(args.steps, spec.steps)
+    model.select(0)
+    dense_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
+    dense_before = timed(dense_loop, steps, args.warmup)
+    t0 = time.time()
+    mode = model.pack()
+    torch.cuda.synchronize()
+    pack_s = time.time() - t0
+    model.select(mode)
+    sparse_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
+    with ClockSampler(local_rank) as clocks:
+        sparse_ms = timed(sparse_loop, steps, args.warmup)
+    if backend.device_status(device) != 0:
+        raise SystemExit("bench: a kernel reported a bounded wait that ran out")
+    dense_after = timed(dense_loop, steps, args.warmup)
+
+    # end to end through the public loop: seeded host noise in, final latent back on the host
+    barrier()
+    begin.record()
+    latent = sparse_loop.run(seed=rank + 100, steps=steps).cpu()
+    end.record()
+    barrier()
+    e2e_ms = begin.elapsed_time(end) / steps
+    projections = len(model.units)
+    if rank == 0:
+        dense_ms = min(dense_before, dense_after)
+        print(json.dumps({
+            "metric": "denoise_step_ms", "value": sparse_ms, "unit": "ms", "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": sparse_ms, "higher_is_better": False, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": args.workload, "mode": f"{mode - 2}:{mode}", "blocks": spec.blocks,
+                       "hidden": spec.hidden, "image_tokens": spec.tokens, "text_tokens": spec.text_tokens,
+                       "cfg_batch": 2 * args.images, "sampler": spec.sampler, "sampler_steps": spec.steps,
+                       "routed_projections": projections, "parallelism": f"data-parallel images x{world}",
+                       "l2": "weights per step exceed L2"},
+            "clocks": clocks.summary(),
+            "dense_bf16": {"ms_before": dense_before, "ms_after": dense_after, "speedup": dense_ms / sparse_ms},
+            "images_per_s": world * args.images / (spec.steps * sparse_ms * 1e-3),
+            "pack_seconds": pack_s,
+            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": latent.numel() * 4 // steps,
+                    "d2h_bytes_per_step": latent.numel() * 4 // steps},
+            "gpu_launches": 2 * projections * steps,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -170,6 +259,10 @@ def main():
     parser.add_argument("--impl", default="native", choices=("native", "reference"))
     parser.add_argument("--tokens", type=str, default=None, help="comma-separated M values (debug)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--workload", default="flux_sweep",
+                        choices=("flux_sweep", "dit-xl-512", "pixart-sigma-1024", "sd35-large-512"))
+    parser.add_argument("--images", type=int, default=1, help="images per forward in the denoise workloads")
+    parser.add_argument("--blocks", type=int, default=None, help="override the block count (debug)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -177,6 +270,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "flux_sweep":
+        run_denoise(args, rank, world, local_rank)
         return
 
     import numpy as np
@@ -300,11 +396,23 @@ def main():
 
     gemm_ms = timed_graph(gemm_only, max(3, args.steps // 2))
     front_ms = timed_graph(frontend_only, max(3, args.steps // 2))
+
+    # paired BF16 dense projection (cuBLAS through torch) over the same calls, for context only
+    dense_w = {(k, n): (0.02 * torch.randn(n, k, device=device)).to(torch.bfloat16) for (k, n) in SHAPES}
+    dense_b = {n: torch.zeros(n, device=device, dtype=torch.bfloat16) for (_, n) in SHAPES}
+
+    def dense_step():
+        return [torch.nn.functional.linear(dev_x[(m, k)], dense_w[(k, n)], dense_b[n]) for (_, k, n, m) in calls]
+
+    dense_ms = timed_graph(dense_step, max(3, args.steps // 2))
+    del dense_w
     pk = peaks()
     sparse_peak = 4.0 * pk["bf16_tflops"]
     gemm_tops = step_ops / (gemm_ms * 1e-3) / 1e12
     executed_ops = sum(2 * (-(-m // 32) * 32) * (-(-n // 32) * 32) * pk_of[(mode, k)] for (mode, k, n, m) in calls)
     executed_tops = executed_ops / (gemm_ms * 1e-3) / 1e12
+    gemm_bytes = sum((-(-m // 32) * 32) * (pk_of[(mode, k)] + 4) + (-(-n // 32) * 32) * (pk_of[(mode, k)] // 2 + pk_of[(mode, k)] // 8)
+                     + 8 * n + 2 * m * n for (mode, k, n, m) in calls)
     front_bytes = sum(2 * m * k + (-(-m // 32) * 32) * (pk_of[(mode, k)] + 4) for (mode, m, k) in quantised)
     front_gbs = front_bytes / (front_ms * 1e-3) / 1e9
 
@@ -385,15 +493,19 @@ def main():
             "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": 2 * len(calls) * args.steps,
             "roofline": {"bound": "tensor", "achieved": gemm_tops, "peak": sparse_peak, "unit": "TFLOP/s",
-                         "frac": gemm_tops / sparse_peak, "traffic": TRAFFIC_BYTES_PER_LAUNCH,
+                         "frac": gemm_tops / sparse_peak, "traffic": TRAFFIC_OVER_ALGORITHMIC * gemm_bytes / len(calls),
+                         "algorithmic_bytes_per_launch": gemm_bytes / len(calls),
                          "executed_tops": executed_tops, "executed_frac": executed_tops / sparse_peak,
                          "executed_frac_of_nominal_9000": executed_tops / 9000.0,
-                         "kernel": "sparse_gemm_kernel (30 launches per step)",
+                         "kernel": "sparse_gemm_pair_kernel (30 launches per step)",
                          "peak_source": f"4 x {pk['source']} dense bf16 {pk['bf16_tflops']} TFLOP/s "
                                         "(2:4-sparse INT8 proxy; nominal 9000)"},
             "roofline_frontend": {"bound": "hbm", "achieved": front_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
                                   "frac": front_gbs / pk["hbm_gbs"], "kernel": "quant_lift_kernel"},
             "cpu_baseline": cpu,
+            "dense_bf16": {"ms_per_step": dense_ms, "tflops": step_ops / (dense_ms * 1e-3) / 1e12,
+                           "sparse_ms_per_step_this_rank": elapsed_ms / args.steps,
+                           "what": "torch.nn.functional.linear (cuBLAS BF16) over the same 30 calls, graph replay"},
             "tp_variant": tp,
         }
         print(json.dumps(line))
