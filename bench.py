@@ -168,6 +168,89 @@ def run_reference(args, rank, world):
     }))
 
 
+# every routed projection shape of the five configurations: (label, mode, M, K, N)
+CONFIG_SHAPES = (
+    ("cfg0 PixArt FFN fc1", 4, 4096, 1152, 4608),
+    ("FLUX QKV", 6, 1536, 3072, 9216), ("FLUX QKV", 8, 1536, 3072, 9216),
+    ("FLUX fc1", 6, 1536, 3072, 12288), ("FLUX fc1", 8, 1536, 3072, 12288),
+    ("FLUX fc2", 6, 1536, 12288, 3072), ("FLUX fc2", 8, 1536, 12288, 3072),
+    ("FLUX QKV M4096", 6, 4096, 3072, 9216), ("FLUX fc1 M16384", 8, 16384, 3072, 12288),
+    ("DiT QKV", 4, 2048, 1152, 3456), ("DiT fc1", 4, 2048, 1152, 4608), ("DiT fc2", 4, 2048, 4608, 1152),
+    ("Sigma QKV", 8, 8192, 1152, 3456), ("Sigma cross-Q", 8, 8192, 1152, 1152), ("Sigma cross-KV", 8, 600, 1152, 2304),
+    ("Sigma fc1", 8, 8192, 1152, 4608), ("Sigma fc2", 8, 8192, 4608, 1152),
+    ("SD3.5 img QKV", 6, 2048, 2432, 7296), ("SD3.5 img fc1", 6, 2048, 2432, 9728), ("SD3.5 img fc2", 6, 2048, 9728, 2432),
+    ("SD3.5 txt QKV", 6, 666, 2432, 7296), ("SD3.5 txt fc1", 6, 666, 2432, 9728), ("SD3.5 txt fc2", 6, 666, 9728, 2432),
+)
+
+
+def run_shapes(args, local_rank):
+    """Per-shape table: complete projection, GEMM alone, front-end alone and the paired BF16 dense
+    projection, each as a CUDA-graph replay over enough independent operand copies to exceed L2."""
+    import torch
+    from __graft_entry__ import load_package, load_oracle
+    sdk = load_package()
+    sdk.load_native()
+    oracle, _ = load_oracle()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    pk = peaks()
+    rows = []
+
+    def timed(fn, calls):
+        s = torch.cuda.Stream(device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            fn()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        for _ in range(max(args.warmup, 3)):
+            g.replay()
+        torch.cuda.synchronize()
+        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b.record()
+        for _ in range(args.steps):
+            g.replay()
+        e.record()
+        torch.cuda.synchronize()
+        return b.elapsed_time(e) * 1e3 / (args.steps * calls)
+
+    for label, mode, m, k, n in CONFIG_SHAPES:
+        _, pkk = sdk.lifted_k(k, mode)
+        per_call = n * pkk * 5 // 8 + m * k * 2 + m * n * 2
+        copies = max(2, min(24, -(-300_000_000 // per_call)))
+        qweight, scales = oracle.make_weight(n, k, mode, seed=n + k + mode)
+        base = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales),
+                                        0.1 * torch.randn(n), mode).to(device)
+        ops = [base] + [sdk.PackedLinear(base.packed.clone(), base.metadata.clone(), base.scales.clone(),
+                                         base.bias.clone(), k, n, mode) for _ in range(copies - 1)]
+        x0 = oracle.make_activation(m, k, seed=m + k).to(device)
+        xs = [x0.clone() for _ in range(copies)]
+        dense_w = [(0.02 * torch.randn(n, k, device=device)).to(torch.bfloat16) for _ in range(copies)]
+        dense_b = torch.zeros(n, device=device, dtype=torch.bfloat16)
+        quantised = [sdk.quantize_lift(x, mode) for x in xs]
+        full_us = timed(lambda: [op(x) for op, x in zip(ops, xs)], copies)
+        gemm_us = timed(lambda: [torch.ops.sdacc_dualscale_sm80.run(q, op.packed, op.metadata, sa, op.scales, op.bias,
+                                                                   m, n, 5, None) for op, (q, sa) in zip(ops, quantised)], copies)
+        front_us = timed(lambda: [torch.ops.sdacc_mild_projection_sm80.quantize(x, mode) for x in xs], copies)
+        dense_us = timed(lambda: [torch.nn.functional.linear(x, w, dense_b) for x, w in zip(xs, dense_w)], copies)
+        pm, pn = -(-m // 32) * 32, -(-n // 32) * 32
+        rows.append({"shape": label, "mode": f"{mode - 2}:{mode}", "m": m, "k": k, "n": n, "copies": copies,
+                     "projection_us": full_us, "gemm_us": gemm_us, "frontend_us": front_us, "dense_bf16_us": dense_us,
+                     "logical_tops": 2.0 * m * n * k / full_us / 1e6,
+                     "gemm_executed_pct_of_9000": 100 * 2.0 * pm * pn * pkk / gemm_us / 1e6 / 9000.0,
+                     "frontend_gbs": (2 * m * k + pm * (pkk + 4)) / front_us / 1e3,
+                     "speedup_vs_dense": dense_us / full_us})
+        del ops, xs, dense_w, quantised, base
+        torch.cuda.empty_cache()
+    print(json.dumps({"metric": "projection_shape_table", "unit": "us", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "data": "synthetic", "dtype": "int8",
+                      "config": {"workload": "shapes", "l2": "operand copies rotate so each step exceeds L2"},
+                      "peaks": pk, "rows": rows}))
+
+
 def run_denoise(args, rank, world, local_rank):
     """Denoise-step latency: sparse routed projections against dense BF16 on the same model."""
     import torch
@@ -260,7 +343,7 @@ def main():
     parser.add_argument("--tokens", type=str, default=None, help="comma-separated M values (debug)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="flux_sweep",
-                        choices=("flux_sweep", "dit-xl-512", "pixart-sigma-1024", "sd35-large-512"))
+                        choices=("flux_sweep", "shapes", "dit-xl-512", "pixart-sigma-1024", "sd35-large-512"))
     parser.add_argument("--images", type=int, default=1, help="images per forward in the denoise workloads")
     parser.add_argument("--blocks", type=int, default=None, help="override the block count (debug)")
     args = parser.parse_args()
@@ -270,6 +353,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "shapes":
+        if rank == 0:
+            run_shapes(args, local_rank)
         return
     if args.workload != "flux_sweep":
         run_denoise(args, rank, world, local_rank)

@@ -199,6 +199,27 @@ __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 32 columns in the matrix-fragment layout: for each group of 8 columns g, thread t
+// holds r[4g+0], r[4g+1] = lane t/4, columns 8g + 2(t%4) and +1; r[4g+2], r[4g+3] = lane t/4 + 8,
+// same columns.  The lane field of taddr selects which 16 lanes of the warp's quadrant.
+__device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+// Four 8x8 matrices of 16-bit elements, transposed on the way: thread t's register i carries, for
+// matrix i, the elements of memory rows 2(t%4) (low half) and 2(t%4)+1 (high half) at position t/4;
+// thread t supplies the address of row t%8 of matrix t/8 (16 bytes per row).
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};"
+               ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }

@@ -526,7 +526,8 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.out_stride) * 2};
     const cuuint32_t box[2] = {32, 32};
-    int rc = encode(&map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    // the epilogue writes its 64-byte rows with the 16-byte pieces XOR-swizzled (bank-conflict-free stmatrix)
+    int rc = encode(&map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
   } else {
     map_out = map_a;       // unused by the direct-store epilogues

@@ -20,7 +20,11 @@
 //                8 epilogue warps of the pair (rank 1 arrives through shared::cluster).
 #pragma once
 
-constexpr int kPairEpiWarps = 8;                       // two warps per TMEM lane quadrant
+#ifndef SS_PAIR_EPI_WARPS
+#define SS_PAIR_EPI_WARPS 8
+#endif
+constexpr int kPairEpiWarps = SS_PAIR_EPI_WARPS;       // 2 or 4 warps per TMEM lane quadrant
+constexpr int kPairSub = kPairEpiWarps / 4;            // warps sharing a quadrant take chunks sub, sub+kPairSub, ...
 constexpr int kPairThreads = 64 + 32 * kPairEpiWarps;
 
 template <int NT, int KB>
@@ -200,10 +204,138 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
     }
+  } else if constexpr (MODE == kOutBf16Tma) {
+    // ------------------------------------------------------------------ epilogue, TMA stores
+    // The accumulator is channel-major in TMEM (lane = channel, column = token) and the output is
+    // token-major.  tcgen05.ld in the 16x256b fragment layout hands each thread two adjacent
+    // tokens of one channel per register pair, which is exactly what stmatrix.trans needs to
+    // write 8 tokens x 8 channels blocks token-major: two values are converted with one packed
+    // BF16 conversion and 32 of them stored with one stmatrix.x4.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
+    const int lane_ch = lane >> 2, tpair = (lane & 3) * 2;
+    uint32_t acc_it = 0, store_it = 0;
+    bool ok = true;
+    constexpr int kSaRegs = (NT + 31) / 32;
+    float sa_next[kSaRegs], sw_next[4], bias_next[4];
+    auto prefetch = [&](int t) {
+      const int pch = (t % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane_ch;
+      const int ptok0 = (t / tiles_ch2) * NT;
+#pragma unroll
+      for (int i = 0; i < kSaRegs; ++i) {
+        const int tok = ptok0 + lane + 32 * i;
+        sa_next[i] = (lane + 32 * i < NT && tok < args.m) ? __ldg(args.sa + tok) : 1.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {               // channels lane_ch + 8 i of the warp's 32
+        const int c = pch + 8 * i;
+        sw_next[i] = c < args.n ? __ldg(args.sw + c) : 1.f;
+        bias_next[i] = (c < args.n && args.bias) ? __ldg(args.bias + c) : 0.f;
+      }
+    };
+    if (pair < num_tiles) prefetch(pair);
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
+      const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
+      const int ch_w = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32;
+      const int tok0 = (tile / tiles_ch2) * NT;
+      float sw[4], bias[4];
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < kSaRegs; ++i)
+        if (lane + 32 * i < NT) sa_s[lane + 32 * i] = sa_next[i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { sw[i] = sw_next[i]; bias[i] = bias_next[i]; }
+      __syncwarp();
+      if (tile + num_pairs < num_tiles) prefetch(tile + num_pairs);
+      int chunks = (args.m - tok0 + 31) / 32;
+      chunks = chunks < NT / 32 ? chunks : NT / 32;
+      if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u)) { ok = false; break; }
+      ptx::tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * NT;
+      auto release = [&]() {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_rank0(&bar_acc_empty[buf]);
+      };
+      auto load = [&](uint32_t (&f)[32], int c) {
+        ptx::tc_ld_16x256b_x4(t_addr + c * 32, f);                       // channels 0..15 of the quadrant
+        ptx::tc_ld_16x256b_x4(t_addr + (16u << 16) + c * 32, f + 16);    // channels 16..31
+      };
+      auto emit = [&](const uint32_t (&f)[32], int c) {
+        uint8_t* stage = smem + T::kOffStore + ((warp - 2) * T::kStoreBufs + (store_it % T::kStoreBufs)) * T::kStoreTile;
+        if (lane == 0) {
+          if constexpr (T::kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
+        }
+        __syncwarp();
+        const float2* sa_c = reinterpret_cast<const float2*>(sa_s + c * 32 + tpair);
+        // this thread addresses row lane%8 of matrix lane/8 in every stmatrix.x4: matrices are
+        // (token group, channel group) = (2 gp, 2 h), (2 gp, 2 h + 1), (2 gp + 1, 2 h), (2 gp + 1, 2 h + 1);
+        // rows are 64 bytes (32 channels) with the 16-byte pieces XOR-swizzled as TMA's 64B mode expects
+        const int mi = lane >> 3;
+        const uint32_t stage_addr = ptx::smem_u32(stage);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int gp = 0; gp < 2; ++gp) {
+            uint32_t packed[4];
+#pragma unroll
+            for (int gi = 0; gi < 2; ++gi) {
+              const int g = 2 * gp + gi;
+              const float2 s = sa_c[4 * g];                                  // tokens 8 g + tpair, + 1
+              const uint32_t* r = f + 16 * h + 4 * g;
+#pragma unroll
+              for (int ab = 0; ab < 2; ++ab) {
+                const float w = sw[2 * h + ab], b = bias[2 * h + ab];
+                const float y0 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab])), __fmul_rn(s.x, w), b);
+                const float y1 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab + 1])), __fmul_rn(s.y, w), b);
+                const __nv_bfloat162 p = __floats2bfloat162_rn(y0, y1);     // low half = even token
+                packed[2 * gi + ab] = *reinterpret_cast<const uint32_t*>(&p);
+              }
+            }
+            const int tok = 8 * (2 * gp + (mi >> 1)) + (lane & 7);
+            const int cg = 2 * h + (mi & 1);
+            ptx::stmatrix_x4_trans(stage_addr + tok * 64 + ((cg ^ ((tok >> 1) & 3)) << 4),
+                                   packed[0], packed[1], packed[2], packed[3]);
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
+          // beyond the last channel is not issued at all
+          if (ch_w < args.n) ptx::tma_store_2d(&map_out, stage, ch_w, tok0 + c * 32);
+          ptx::bulk_commit();
+        }
+        ++store_it;
+      };
+      const int mine = chunks > half ? (chunks - half + kPairSub - 1) / kPairSub : 0;
+      if (mine == 0) {
+        release();
+      } else {
+        uint32_t f0[32], f1[32];
+        load(f0, half);
+#pragma unroll 1
+        for (int i = 0; i < mine; i += 2) {
+          const int c = half + kPairSub * i;
+          ptx::tc_wait_ld();
+          if (i + 1 < mine) load(f1, c + kPairSub); else release();
+          emit(f0, c);
+          if (i + 1 < mine) {
+            ptx::tc_wait_ld();
+            if (i + 2 < mine) load(f0, c + 2 * kPairSub); else release();
+            emit(f1, c + kPairSub);
+          }
+        }
+      }
+    }
+    if (lane == 0) ptx::bulk_wait_all();
+    __syncwarp();
+    if (!ok && lane == 0) atomicOr(args.status, kStatusEpilogueTimeout);
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int quad = warp & 3;                    // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;             // the quadrant's two warps take alternate chunks
+    const int half = (warp - 2) >> 2;             // which of the quadrant's warps: chunks half, half+kPairSub, ...
     float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
     uint32_t acc_it = 0, store_it = 0;
     bool ok = true;
@@ -314,21 +446,21 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           store_chunk<INT32_OUT, HAS_ADDEND>(r, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
         }
       };
-      const int mine = chunks > half ? (chunks - half + 1) / 2 : 0;      // chunks half, half+2, ...
+      const int mine = chunks > half ? (chunks - half + kPairSub - 1) / kPairSub : 0;
       if (mine == 0) {
         release();
       } else {
         ptx::tc_ld_32x32b_x32(t_addr + half * 32, r0);
 #pragma unroll 1
         for (int i = 0; i < mine; i += 2) {
-          const int c = half + 2 * i;
+          const int c = half + kPairSub * i;
           ptx::tc_wait_ld();
-          if (i + 1 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + 2) * 32, r1); else release();
+          if (i + 1 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + kPairSub) * 32, r1); else release();
           emit(r0, c);
           if (i + 1 < mine) {
             ptx::tc_wait_ld();
-            if (i + 2 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + 4) * 32, r0); else release();
-            emit(r1, c + 2);
+            if (i + 2 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + 2 * kPairSub) * 32, r0); else release();
+            emit(r1, c + kPairSub);
           }
         }
       }

@@ -23,8 +23,8 @@ def test_pack_members_matches_host_preparation_and_oracle(mods, sdk, oracle, mod
     torch.manual_seed(mode)
     members = [torch.nn.Linear(k, w).to(DEV, torch.bfloat16) for w in widths]
     op = routing.pack_members(members, mode)
-    weight = torch.cat([m.weight for m in members]).float().cpu().numpy()
-    bias = torch.cat([m.bias for m in members]).float().cpu().numpy()
+    weight = torch.cat([m.weight for m in members]).detach().float().cpu().numpy()
+    bias = torch.cat([m.bias for m in members]).detach().float().cpu().numpy()
     pruned, _ = oracle.magnitude_prune(weight, mode)
     qweight, scales = oracle.weight_grid(pruned)
     assert np.array_equal(op.scales.cpu().numpy(), scales)
@@ -35,7 +35,8 @@ def test_pack_members_matches_host_preparation_and_oracle(mods, sdk, oracle, mod
     x = oracle.make_activation(70, k, seed=mode)
     state = routing.ProjectionState(members, {mode: op})
     state.select(mode)
-    outs = state.members_output(x.to(DEV))
+    with torch.no_grad():
+        outs = state.members_output(x.to(DEV))
     expect = oracle.projection(x, qweight, scales, bias, mode)["out_bits"]
     assert np.array_equal(bits(torch.cat(outs, -1)), expect)
 
