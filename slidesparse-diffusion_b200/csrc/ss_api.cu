@@ -140,6 +140,7 @@ extern "C" int ss_projection(const void* x, int64_t sx, int64_t m, int64_t k, in
   if (int rc = launch_quantize_lift(x, sx, m, k, group, q_scratch, sa_scratch, s)) return rc;
   GemmArgs a{q_scratch, packed, meta, sa_scratch, sw, bias, addend, addend_stride, out,
              out_stride, m, n, pm, pn, pk, false};
+  a.overlap_prologue = true;
   return launch_gemm(a, s);
 }
 
@@ -189,6 +190,7 @@ extern "C" int ss_plan_run(int64_t handle, const void* x, int64_t sx, int8_t* q_
   if (int rc = launch_quantize_lift(x, sx, plan->m, plan->k, plan->group, q, sa, s)) return rc;
   GemmArgs a{q, plan->packed, plan->meta, sa, plan->sw, plan->bias, nullptr, 0, out, out_stride,
              plan->m, plan->n, plan->pm, plan->pn, plan->pk, false};
+  a.overlap_prologue = true;
   return launch_gemm(a, s);
 }
 

@@ -55,6 +55,10 @@ struct GemmArgs {
   int64_t out_stride;
   int64_t m, n, pm, pn, pk;
   bool int32_out;
+  // the launch directly follows the front-end that produces q and sa in the same stream: the
+  // kernel may start (set-up, weight prefetch) before that grid has finished and waits on the
+  // device before it touches q, sa or out
+  bool overlap_prologue = false;
 };
 struct GemmResources {
   int threads, smem, regs, local, ctas_per_sm, token_tile, stages, tmem_cols;
@@ -220,6 +224,11 @@ __device__ __forceinline__ void stmatrix_x4_trans(uint32_t saddr, uint32_t a, ui
                ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d)
                : "memory");
 }
+// Programmatic dependent launch: a kernel launched with programmatic stream serialization may
+// start once every CTA of the preceding kernel has called grid_dep_launch (or exited); it must
+// call grid_dep_wait before touching anything that kernel writes.  Both are no-ops otherwise.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }

@@ -70,6 +70,9 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
   __shared__ uint32_t warp_max[32];
   __shared__ float warp_fmax[32];
   __shared__ float s_inv;
+  // lets a GEMM launched with programmatic stream serialization run its set-up while the last
+  // wave of rows is still being quantised (it waits on the device before reading q or sa)
+  ptx::grid_dep_launch();
   __shared__ uint32_t s_bits;
 
   const int row = blockIdx.x, t = threadIdx.x, T = blockDim.x;

@@ -473,6 +473,12 @@ int launch_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t st
   return launch_t<NT, KB, false, false>(a, dev, cfg_index, stream);
 }
 
+// SS_PDL=0 switches the overlapped GEMM prologue off (plain stream order).
+bool pdl_enabled() {
+  const char* env = std::getenv("SS_PDL");
+  return !(env && std::atoi(env) == 0);
+}
+
 // ---- CTA-pair launcher -----------------------------------------------------------------------
 template <int NT, int KB, int MODE>
 int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
@@ -532,7 +538,17 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   } else {
     map_out = map_a;       // unused by the direct-store epilogues
   }
-  kernel<<<grid, kPairThreads, T::kSmemBytes, stream>>>(map_a, map_b, map_e, map_out, k);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kPairThreads);
+  cfg.dynamicSmemBytes = T::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.overlap_prologue && pdl_enabled() ? 1 : 0;
+  SS_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_e, map_out, k));
   SS_CUDA(cudaGetLastError());
   return SS_OK;
 }

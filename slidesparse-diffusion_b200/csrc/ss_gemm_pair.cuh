@@ -126,6 +126,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     if (lane == 0) {
       uint32_t issued = 0;
       bool ok = true;
+      ptx::grid_dep_wait();           // q is written by the kernel launched just before this one
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int ch0 = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
         const int tok0 = (tile / tiles_ch2) * NT + static_cast<int>(rank) * T::kHalf;
@@ -234,6 +235,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         bias_next[i] = (c < args.n && args.bias) ? __ldg(args.bias + c) : 0.f;
       }
     };
+    ptx::grid_dep_wait();             // sa is written by the kernel launched just before this one
     if (pair < num_tiles) prefetch(pair);
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
@@ -358,6 +360,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (args.bias) bias_next = __ldg(args.bias + pch);
       }
     };
+    ptx::grid_dep_wait();
     if constexpr (!INT32_OUT) {
       if (pair < num_tiles) prefetch(pair);
     }
