@@ -296,6 +296,9 @@ def run_denoise(args, rank, world, local_rank):
     torch.cuda.synchronize()
     pack_s = time.time() - t0
     model.select(mode)
+    plain_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
+    sparse_plain_ms = timed(plain_loop, steps, args.warmup)      # neighbours as separate PyTorch kernels
+    model.fuse_neighbours(True)                                  # LayerNorm+modulate and GELU inside the front-end
     sparse_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
     with ClockSampler(local_rank) as clocks:
         sparse_ms = timed(sparse_loop, steps, args.warmup)
@@ -323,7 +326,10 @@ def run_denoise(args, rank, world, local_rank):
                        "routed_projections": projections, "parallelism": f"data-parallel images x{world}",
                        "l2": "weights per step exceed L2"},
             "clocks": clocks.summary(),
-            "dense_bf16": {"ms_before": dense_before, "ms_after": dense_after, "speedup": dense_ms / sparse_ms},
+            "dense_bf16": {"ms_before": dense_before, "ms_after": dense_after, "speedup": dense_ms / sparse_ms,
+                           "what": "same model, routed projections as BF16 nn.Linear, neighbours as PyTorch kernels"},
+            "sparse_unfused_neighbours": {"ms": sparse_plain_ms, "speedup_vs_dense": dense_ms / sparse_plain_ms,
+                                          "what": "sparse projections with LayerNorm+modulate and GELU left to PyTorch"},
             "images_per_s": world * args.images / (spec.steps * sparse_ms * 1e-3),
             "pack_seconds": pack_s,
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": latent.numel() * 4 // steps,

@@ -119,6 +119,37 @@ int ss_projection(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k
                   int8_t* q_scratch, float* sa_scratch,
                   void* out_bf16, int64_t out_row_stride, void* stream);
 
+/* Front-end with a fused element-wise prologue, and the projection built on it.
+ * No counterpart in the reference, which runs these neighbours of the projection as separate PyTorch kernels
+ * (adaLN-modulated LayerNorm before QKV / FFN-in, GELU before FFN-out): the row is rewritten in
+ * registers before it is quantised, so the neighbour costs no extra pass over HBM.
+ *   prologue 0  none (identical to ss_quantize_lift / ss_projection)
+ *   prologue 1  y = ((x - mean) * rstd) * (1 + scale[b]) + shift[b], mean / biased variance over
+ *               the k elements of the row, rstd = 1 / sqrt(var + eps), b = row / rows_per_batch;
+ *               shift, scale: BF16 [ceil(m / rows_per_batch), k], rows mod_row_stride elements
+ *               apart (>= k, multiple of 8), 16-byte aligned
+ *   prologue 2  y = gelu_tanh(x) = 0.5 x (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))
+ * y is rounded to BF16 and then quantised exactly as ss_quantize_lift quantises a BF16 input.
+ * Needs 16-byte aligned rows and k % 8 == 0.  Prologue 1 uses separately rounded fp32 operations
+ * in a fixed order, which the numpy oracle restates bit for bit; prologue 2 uses the hardware tanh
+ * approximation (relative error 2^-11) and is exact to floating-point tolerance only:
+ * |y - gelu_tanh(x)| <= 2.5e-4 |x| before the BF16 rounding. */
+int ss_quantize_lift_fused(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k, int group,
+                           int prologue, const void* shift_bf16, const void* scale_bf16,
+                           int64_t mod_row_stride, int64_t rows_per_batch, float eps,
+                           int8_t* q, float* sa, void* stream);
+/* ss_quantize_lift_fused followed by the GEMM.  No counterpart in the reference (see above);
+ * the remaining arguments are those of ss_projection. */
+int ss_projection_fused(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k, int group,
+                        int prologue, const void* shift_bf16, const void* scale_bf16,
+                        int64_t mod_row_stride, int64_t rows_per_batch, float eps,
+                        const int8_t* packed, const int32_t* meta_b200,
+                        const float* sw, const float* bias,
+                        const void* addend_bf16, int64_t addend_row_stride,
+                        int64_t n, int64_t pn,
+                        int8_t* q_scratch, float* sa_scratch,
+                        void* out_bf16, int64_t out_row_stride, void* stream);
+
 /* The complete projection (front-end + GEMM, no addend) for callers that cannot allocate device
  * memory at all: hosts whose HBM is fully carved into their own pools, loops in which
  * cudaMalloc/cudaFree are banned because they lock, block and may fail, plug-ins without access

@@ -193,6 +193,112 @@ def quantize_lift(x, mode):
     return q, sa
 
 
+# ---- fused front-end prologues (an extension of this build; the reference has no counterpart) ----
+# LayerNorm + modulation: the GPU kernel uses separately rounded fp32 operations in a fixed order,
+# restated here operation for operation (numpy float32 arithmetic is IEEE round-to-nearest like the
+# device's __fadd_rn / __fmul_rn / __fdiv_rn / __fsqrt_rn), so parity is bit-exact.  GELU: see below.
+
+def _f32(v):
+    return np.float32(v)
+
+
+def _bf16_round_f32(y):
+    """fp32 -> nearest-even BF16, returned as fp32 values."""
+    return torch.from_numpy(np.ascontiguousarray(y, dtype=np.float32)).to(torch.bfloat16).float().numpy()
+
+
+def prologue_gelu(x):
+    """BF16 [m,k] -> gelu_tanh(x) = x * sigmoid(2 sqrt(2/pi) (x + 0.044715 x^3)) in fp32, rounded to
+    BF16 (fp32 values).  The GPU uses the hardware tanh approximation (relative error 2^-11), so
+    parity of this prologue is within floating-point tolerance: |error| <= 2.5e-4 |x| before the
+    BF16 rounding."""
+    xf = _bf16_to_f32(x)
+    with np.errstate(invalid="ignore", over="ignore"):
+        x2 = (xf * xf).astype(np.float32)
+        u2 = (xf * (_f32(1.5957691216057308) + _f32(0.07135481627260025) * x2).astype(np.float32)).astype(np.float32)
+        sig = (_f32(1.0) / (_f32(1.0) + np.exp(-u2, dtype=np.float32)).astype(np.float32)).astype(np.float32)
+        y = (xf * sig).astype(np.float32)
+    return _bf16_round_f32(y)
+
+
+def frontend_threads(k, mode):
+    """(threads per row, 16-byte vectors per chunk, chunks per thread) of the front-end kernel."""
+    l = group_size(mode)
+    cv = {4: 2, 6: 3, 8: 4}[l]
+    ow = {4: 4, 6: 8, 8: 12}[l]
+    per_thread = 8 // cv
+    _, pk = lifted_k(k, l)
+    nvec = -(-k // 8)
+    chunks = max(-(-nvec // cv), -(-(pk // 4) // ow))
+    threads = 32
+    while threads * per_thread < chunks:
+        threads *= 2
+    return threads, cv, per_thread
+
+
+def _block_sum(values, valid, threads, cv, per_thread):
+    """Row sums in the kernel's order: each thread adds its elements sequentially (chunk i, vector c,
+    element 0..7 at vector index (t + i*threads)*cv + c), lanes combine by xor butterfly 16..1, then
+    the warp totals combine the same way.  values: fp32 [m, nvec*8]; valid: element mask or None."""
+    m, width = values.shape
+    nvec = width // 8
+    part = np.zeros((m, threads), dtype=np.float32)
+    t = np.arange(threads)
+    for i in range(per_thread):
+        for c in range(cv):
+            idx = (t + i * threads) * cv + c
+            ok = idx < nvec
+            cols = np.where(ok, idx, 0) * 8
+            for e in range(8):
+                add = np.where(ok[None, :], values[:, cols + e], _f32(0.0)).astype(np.float32)
+                if valid is not None:
+                    add = np.where(valid[cols + e][None, :], add, _f32(0.0))
+                part = (part + add).astype(np.float32)
+    warps = threads // 32
+    lanes = part.reshape(m, warps, 32)
+    lane = np.arange(32)
+    for d in (16, 8, 4, 2, 1):
+        lanes = (lanes + lanes[:, :, lane ^ d]).astype(np.float32)
+    totals = np.zeros((m, 32), dtype=np.float32)
+    totals[:, :warps] = lanes[:, :, 0]
+    for d in (16, 8, 4, 2, 1):
+        totals = (totals + totals[:, lane ^ d]).astype(np.float32)
+    return totals[:, 0]
+
+
+def prologue_norm_modulate(x, shift, scale, rows_per_batch, eps, mode):
+    """BF16 [m,k] -> ((x - mean) * rstd) * (1 + scale[b]) + shift[b], b = row // rows_per_batch,
+    rounded to BF16 (fp32 values).  mean and biased variance are block sums in the kernel's order
+    (which depends on the mode through the thread layout); rstd = 1 / sqrt(var + eps)."""
+    xf = _bf16_to_f32(x)
+    m, k = xf.shape
+    if k % 8:
+        raise ValueError("k % 8 == 0 required")
+    sh, sc = _bf16_to_f32(shift), _bf16_to_f32(scale)
+    threads, cv, per_thread = frontend_threads(k, mode)
+    kf = _f32(k)
+    mean = (_block_sum(xf, None, threads, cv, per_thread) / kf).astype(np.float32)
+    dev = (xf - mean[:, None]).astype(np.float32)
+    var = (_block_sum((dev * dev).astype(np.float32), None, threads, cv, per_thread) / kf).astype(np.float32)
+    rstd = (_f32(1.0) / np.sqrt((var + _f32(eps)).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    b = np.arange(m) // rows_per_batch
+    y = (dev * rstd[:, None]).astype(np.float32)
+    y = (y * (_f32(1.0) + sc[b]).astype(np.float32)).astype(np.float32)
+    y = (y + sh[b]).astype(np.float32)
+    return _bf16_round_f32(y)
+
+
+def quantize_lift_fused(x, mode, prologue, shift=None, scale=None, rows_per_batch=1, eps=1e-6):
+    """The fused front-end: prologue ('gelu' | 'norm_modulate' | None), then quantize_lift."""
+    if prologue == "gelu":
+        y = prologue_gelu(x)
+    elif prologue == "norm_modulate":
+        y = prologue_norm_modulate(x, shift, scale, rows_per_batch, eps, mode)
+    else:
+        return quantize_lift(x, mode)
+    return quantize_lift(torch.from_numpy(y).to(torch.bfloat16), mode)
+
+
 def gemm_int32(q, lifted, m=None):
     """acc[m,n] = q[:m] . lifted^T in exact int32 (lifted: [n,kl], kl <= pk)."""
     q = np.asarray(q, dtype=np.int8)

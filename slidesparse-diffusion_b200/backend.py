@@ -100,6 +100,9 @@ def _declare(lib):
         "ss_gemm_run": [vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, i64, vp],
         "ss_gemm_int32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp],
         "ss_projection": [vp, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, vp],
+        "ss_quantize_lift_fused": [vp, i64, i64, i64, i32, i32, vp, vp, i64, i64, c.c_float, vp, vp, vp],
+        "ss_projection_fused": [vp, i64, i64, i64, i32, i32, vp, vp, i64, i64, c.c_float,
+                                vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, vp],
         "ss_projection_static": [vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, i64, vp, i64, vp],
         "ss_plan_create": [vp, vp, vp, vp, i64, i64, i64, i64, i32, vp],
         "ss_plan_run": [i64, vp, i64, vp, vp, vp, i64, vp],
@@ -314,6 +317,113 @@ def _projection(input, packed, metadata, scales, bias, group, n, config, output_
                                       _ptr(scales), _ptr(bias), _ptr(addend),
                                       addend.stride(0) if addend is not None else 0, n, pn,
                                       _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
+    return out
+
+
+PROLOGUES = {"none": 0, "norm_modulate": 1, "gelu": 2}
+
+
+class Prologue:
+    """Element-wise neighbour fused into the front-end (an extension; the reference has none).
+
+    Prologue.norm_modulate(shift, scale, eps): LayerNorm without affine over the last dimension,
+    then x * (1 + scale[b]) + shift[b]; shift / scale are BF16 [batch, k] for an input [batch, rows, k].
+    Prologue.gelu(): tanh-approximated GELU."""
+
+    def __init__(self, kind, shift=None, scale=None, eps=1e-6):
+        if kind not in PROLOGUES:
+            raise ValueError("unknown prologue")
+        self.kind, self.shift, self.scale, self.eps = kind, shift, scale, float(eps)
+
+    @classmethod
+    def norm_modulate(cls, shift, scale, eps=1e-6):
+        return cls("norm_modulate", shift, scale, eps)
+
+    @classmethod
+    def gelu(cls):
+        return cls("gelu")
+
+    def torch_reference(self, x):
+        """The same neighbour as separate PyTorch operators (what a dense path runs)."""
+        if self.kind == "gelu":
+            return torch.nn.functional.gelu(x, approximate="tanh")
+        if self.kind == "norm_modulate":
+            xn = torch.nn.functional.layer_norm(x, x.shape[-1:], eps=self.eps)
+            return torch.addcmul(self.shift[:, None], xn, 1 + self.scale[:, None])
+        return x
+
+    def arguments(self, x, k):
+        """(code, shift, scale, row stride of shift/scale, rows_per_batch, eps) for the C entry."""
+        if self.kind != "norm_modulate":
+            return PROLOGUES[self.kind], None, None, 0, 1, 0.0
+        if x.ndim != 3:
+            raise ValueError("norm_modulate needs [batch, rows, k] input")
+        batch, rows = x.shape[0], x.shape[1]
+        shift, scale = self.shift, self.scale
+        for t in (shift, scale):
+            if t is None or t.dtype != torch.bfloat16 or t.device != x.device or tuple(t.shape) != (batch, k):
+                raise ValueError("shift / scale must be BF16 [batch, k] on the input's device")
+        usable = all(t.stride(1) == 1 and t.data_ptr() % 16 == 0 and t.stride(0) % 8 == 0 and t.stride(0) >= k
+                     for t in (shift, scale)) and (batch == 1 or shift.stride(0) == scale.stride(0))
+        if not usable:
+            shift, scale = shift.contiguous(), scale.contiguous()
+        return 1, shift, scale, (shift.stride(0) if batch > 1 else k), rows, self.eps
+
+
+def _fused_frontend_args(input, prologue):
+    k = input.shape[-1]
+    code, shift, scale, mod_stride, rows, eps = prologue.arguments(input, k)
+    flat = _flatten_input(input, k)
+    if code and (flat.data_ptr() % 16 or flat.stride(0) % 8 or k % 8):
+        flat = flat.contiguous()
+        if flat.data_ptr() % 16 or k % 8:
+            raise ValueError("a prologue needs k % 8 == 0")
+    return flat, code, shift, scale, mod_stride, rows, eps
+
+
+def quantize_lift_fused(input, group, prologue):
+    """Front-end with a prologue: (q int8 [pm,pk], scales fp32 [pm])."""
+    if not input.is_cuda or input.dtype != torch.bfloat16:
+        raise ValueError("BF16 CUDA input required")
+    group = group_size(int(group))
+    flat, code, shift, scale, mod_stride, rows, eps = _fused_frontend_args(input, prologue)
+    m, k = flat.shape
+    _, pk = lifted_k(k, group)
+    pm = -(-m // 32) * 32
+    q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
+    sa = torch.empty(pm, dtype=torch.float32, device=input.device)
+    with torch.cuda.device(input.device):
+        check(library().ss_quantize_lift_fused(_ptr(flat), flat.stride(0), m, k, group, code, _ptr(shift), _ptr(scale),
+                                               mod_stride, rows, eps, _ptr(q), _ptr(sa), _stream(input.device)))
+    return q, sa
+
+
+def projection_fused(input, prologue, packed, metadata, scales, bias, group, n, output_addend=None):
+    """`projection` with the prologue applied to the input inside the front-end kernel."""
+    if not input.is_cuda or input.dtype != torch.bfloat16 or input.ndim < 1:
+        raise ValueError("BF16 CUDA input required")
+    group = group_size(int(group))
+    flat, code, shift, scale, mod_stride, rows, eps = _fused_frontend_args(input, prologue)
+    m, k = flat.shape
+    if m <= 0:
+        raise ValueError("empty input unsupported by native frontend")
+    _, pk = lifted_k(k, group)
+    pm = -(-m // 32) * 32
+    _check_weights(input.device, packed, metadata, scales, bias, pk)
+    pn = packed.shape[0]
+    if not (0 < n <= pn and scales.numel() >= n and (bias.numel() == 0 or bias.numel() >= n)):
+        raise ValueError("original dimensions/channels")
+    addend = output_addend
+    if addend is not None:
+        addend = _check_addend(addend.reshape(-1, n), input.device, m, n)
+    q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
+    sa = torch.empty(pm, dtype=torch.float32, device=input.device)
+    out = torch.empty((*input.shape[:-1], n), dtype=torch.bfloat16, device=input.device)
+    with torch.cuda.device(input.device):
+        check(library().ss_projection_fused(_ptr(flat), flat.stride(0), m, k, group, code, _ptr(shift), _ptr(scale),
+                                            mod_stride, rows, eps, _ptr(packed), _ptr(metadata), _ptr(scales), _ptr(bias),
+                                            _ptr(addend), addend.stride(0) if addend is not None else 0, n, pn,
+                                            _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
     return out
 
 

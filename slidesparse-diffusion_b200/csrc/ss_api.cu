@@ -144,6 +144,34 @@ extern "C" int ss_projection(const void* x, int64_t sx, int64_t m, int64_t k, in
   return launch_gemm(a, s);
 }
 
+extern "C" int ss_quantize_lift_fused(const void* x, int64_t sx, int64_t m, int64_t k, int group,
+                                      int prologue, const void* shift, const void* scale,
+                                      int64_t mod_stride, int64_t rows_per_batch, float eps,
+                                      int8_t* q, float* sa, void* stream) {
+  return launch_quantize_lift_fused(x, sx, m, k, group, prologue, shift, scale, mod_stride, rows_per_batch,
+                                    eps, q, sa, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ss_projection_fused(const void* x, int64_t sx, int64_t m, int64_t k, int group,
+                                   int prologue, const void* shift, const void* scale,
+                                   int64_t mod_stride, int64_t rows_per_batch, float eps,
+                                   const int8_t* packed,
+                                   const int32_t* meta, const float* sw, const float* bias,
+                                   const void* addend, int64_t addend_stride, int64_t n, int64_t pn,
+                                   int8_t* q_scratch, float* sa_scratch, void* out,
+                                   int64_t out_stride, void* stream) {
+  int64_t pm, pk;
+  if (int rc = check_projection_shape(m, k, n, pn, group, &pm, &pk)) return rc;
+  SS_REQUIRE(q_scratch && sa_scratch, SS_E_ARG, "projection: scratch buffers required");
+  auto s = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_quantize_lift_fused(x, sx, m, k, group, prologue, shift, scale, mod_stride,
+                                          rows_per_batch, eps, q_scratch, sa_scratch, s)) return rc;
+  GemmArgs a{q_scratch, packed, meta, sa_scratch, sw, bias, addend, addend_stride, out,
+             out_stride, m, n, pm, pn, pk, false};
+  a.overlap_prologue = true;
+  return launch_gemm(a, s);
+}
+
 extern "C" int ss_plan_create(const int8_t* packed, const int32_t* meta, const float* sw,
                               const float* bias, int64_t k, int64_t m, int64_t n, int64_t pn,
                               int group, int64_t* handle) {

@@ -41,6 +41,9 @@ uint32_t* device_status_ptr();   // address of the status word on the current de
 // ---- entry points implemented per kernel file -------------------------------------------
 int launch_quantize_lift(const void* x, int64_t sx, int64_t m, int64_t k, int group,
                          int8_t* q, float* sa, cudaStream_t stream);
+int launch_quantize_lift_fused(const void* x, int64_t sx, int64_t m, int64_t k, int group, int prologue,
+                               const void* shift, const void* scale, int64_t mod_stride,
+                               int64_t rows_per_batch, float eps, int8_t* q, float* sa, cudaStream_t stream);
 
 struct GemmArgs {
   const int8_t* q;

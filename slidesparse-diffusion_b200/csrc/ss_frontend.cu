@@ -15,6 +15,7 @@
 // Rows that contain Inf or NaN (detected from the same packed maximum) take an element-wise path
 // that reproduces the reference's fmaxf/fminf conventions bit for bit.  No fast-math.
 #include "ss_common.cuh"
+#include <cuda_bf16.h>
 
 namespace ss {
 namespace {
@@ -43,6 +44,57 @@ __device__ __forceinline__ uint32_t quant4_fast(uint32_t a, uint32_t b, float in
   return out;
 }
 
+// ---- optional prologues (an extension; the reference front-end has none) -----------------------
+// A prologue rewrites the row, in registers, before it is quantised, so that an element-wise
+// neighbour of the projection costs no extra pass over HBM:
+//   kProNormModulate  y = ((x - mean) * rstd) * (1 + scale[b]) + shift[b]   (LayerNorm without affine,
+//                     then the adaLN modulation of the row's batch b = row / rows_per_batch)
+//   kProGelu          y = gelu_tanh(x)
+// y is rounded to BF16 and everything downstream sees exactly those BF16 values.  In
+// kProNormModulate every step is a separately rounded fp32 add / multiply / divide / sqrt in a fixed
+// order (no fused multiply-add), so a host restatement reproduces the result bit for bit; kProGelu
+// uses the hardware tanh approximation and is reproduced within floating-point tolerance.
+enum : int { kProNone = 0, kProNormModulate = 1, kProGelu = 2 };
+struct Prologue {
+  const uint16_t* shift;     // BF16 [batches, k], rows mod_stride elements apart
+  const uint16_t* scale;     // BF16 [batches, k], rows mod_stride elements apart
+  int64_t mod_stride;
+  int rows_per_batch;
+  float eps;
+};
+
+__device__ __forceinline__ uint32_t bf16_rn_bits(float f) {
+  return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(f)));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  return bf16_rn_bits(lo) | (bf16_rn_bits(hi) << 16);
+}
+// gelu_tanh(x) = 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3), with the hardware tanh
+// (tanh.approx.f32: relative error 2^-11, one special-function instruction per element; a second
+// one per element would make that unit the bound of the whole kernel).  Floating point within
+// tolerance: |error| <= |x| * 2.5e-4, below the BF16 rounding that follows except in the negative
+// tail, where |gelu| < 4e-3 anyway.
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float x2 = __fmul_rn(x, x);
+  const float u = __fmul_rn(x, __fmaf_rn(x2, 0.035677408f, 0.79788456f));
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  const float h = __fmul_rn(0.5f, x);
+  return __fmaf_rn(h, t, h);
+}
+// Block-wide sum with a fixed order: lanes by xor butterfly, then the warp totals the same way.
+__device__ __forceinline__ float block_sum(float a, float* scratch, int t, int nthreads) {
+#pragma unroll
+  for (int d = 16; d; d >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, d));
+  __syncthreads();                                   // scratch may still be read from a previous call
+  if ((t & 31) == 0) scratch[t >> 5] = a;
+  __syncthreads();
+  float b = (t & 31) < (nthreads >> 5) ? scratch[t & 31] : 0.f;
+#pragma unroll
+  for (int d = 16; d; d >>= 1) b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, d));
+  return b;
+}
+
 template <int L> struct Chunk;
 template <> struct Chunk<4> { static constexpr int kVec = 2, kOutWords = 4; };
 template <> struct Chunk<6> { static constexpr int kVec = 3, kOutWords = 8; };
@@ -61,19 +113,19 @@ __device__ __forceinline__ void lift_chunk(const uint32_t* qw, uint32_t* ow) {
     }
 }
 
-// L: group size (4, 6, 8).  VEC: rows are 16-byte aligned and k % 8 == 0.
-template <int L, bool VEC>
+// L: group size (4, 6, 8).  VEC: rows are 16-byte aligned and k % 8 == 0.  PRO: prologue (VEC only).
+template <int L, bool VEC, int PRO = kProNone>
 __global__ void __launch_bounds__(kMaxThreads)
 quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict__ q,
-                  float* __restrict__ sa, int m, int k, int pk, int nvec) {
+                  float* __restrict__ sa, int m, int k, int pk, int nvec, const Prologue pro) {
   constexpr int CV = Chunk<L>::kVec, OW = Chunk<L>::kOutWords, kChunks = kMaxVec / CV;
   __shared__ uint32_t warp_max[32];
   __shared__ float warp_fmax[32];
   __shared__ float s_inv;
+  __shared__ uint32_t s_bits;
   // lets a GEMM launched with programmatic stream serialization run its set-up while the last
   // wave of rows is still being quantised (it waits on the device before reading q or sa)
   ptx::grid_dep_launch();
-  __shared__ uint32_t s_bits;
 
   const int row = blockIdx.x, t = threadIdx.x, T = blockDim.x;
   const bool live = row < m;
@@ -101,10 +153,84 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
         }
       }
       v[i][c] = w;
+    }
+  }
+  if constexpr (PRO == kProGelu) {
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+      for (int c = 0; c < CV; ++c) {
+        uint4& w = v[i][c];
+        w.x = pack_bf16(gelu_tanh(bf_lo(w.x)), gelu_tanh(bf_hi(w.x)));
+        w.y = pack_bf16(gelu_tanh(bf_lo(w.y)), gelu_tanh(bf_hi(w.y)));
+        w.z = pack_bf16(gelu_tanh(bf_lo(w.z)), gelu_tanh(bf_hi(w.z)));
+        w.w = pack_bf16(gelu_tanh(bf_lo(w.w)), gelu_tanh(bf_hi(w.w)));
+      }
+  }
+  if constexpr (PRO == kProNormModulate) {
+    // mean and variance over the k valid elements (two passes over the registers)
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+      for (int c = 0; c < CV; ++c) {
+        const uint4 w = v[i][c];
+        const uint32_t e[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) part = __fadd_rn(__fadd_rn(part, bf_lo(e[j])), bf_hi(e[j]));
+      }
+    const float kf = static_cast<float>(k);
+    const float mean = __fdiv_rn(block_sum(part, warp_fmax, t, T), kf);
+    part = 0.f;
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+      for (int c = 0; c < CV; ++c) {
+        if ((t + i * T) * CV + c < nvec) {
+          const uint4 w = v[i][c];
+          const uint32_t e[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float d0 = __fadd_rn(bf_lo(e[j]), -mean), d1 = __fadd_rn(bf_hi(e[j]), -mean);
+            part = __fadd_rn(__fadd_rn(part, __fmul_rn(d0, d0)), __fmul_rn(d1, d1));
+          }
+        }
+      }
+    const float var = __fdiv_rn(block_sum(part, warp_fmax, t, T), kf);
+    const float rstd = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(var, pro.eps)));
+    const int64_t brow = static_cast<int64_t>(live ? row / pro.rows_per_batch : 0) * pro.mod_stride;
+    const uint4* shift = reinterpret_cast<const uint4*>(pro.shift + brow);
+    const uint4* scale = reinterpret_cast<const uint4*>(pro.scale + brow);
+#pragma unroll
+    for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+      for (int c = 0; c < CV; ++c) {
+        const int idx = (t + i * T) * CV + c;
+        if (live && idx < nvec) {
+          uint4& w = v[i][c];
+          const uint4 sh = __ldg(shift + idx), sc = __ldg(scale + idx);
+          uint32_t e[4] = {w.x, w.y, w.z, w.w};
+          const uint32_t hs[4] = {sh.x, sh.y, sh.z, sh.w}, cs[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float y0 = __fadd_rn(__fmul_rn(__fmul_rn(__fadd_rn(bf_lo(e[j]), -mean), rstd),
+                                                 __fadd_rn(1.f, bf_lo(cs[j]))), bf_lo(hs[j]));
+            const float y1 = __fadd_rn(__fmul_rn(__fmul_rn(__fadd_rn(bf_hi(e[j]), -mean), rstd),
+                                                 __fadd_rn(1.f, bf_hi(cs[j]))), bf_hi(hs[j]));
+            e[j] = pack_bf16(y0, y1);
+          }
+          w = make_uint4(e[0], e[1], e[2], e[3]);
+        }
+      }
+  }
+#pragma unroll
+  for (int i = 0; i < kChunks; ++i)
+#pragma unroll
+    for (int c = 0; c < CV; ++c) {
+      const uint4 w = v[i][c];
       imax = __vmaxu2(imax, __vmaxu2(__vmaxu2(w.x & 0x7fff7fffu, w.y & 0x7fff7fffu),
                                      __vmaxu2(w.z & 0x7fff7fffu, w.w & 0x7fff7fffu)));
     }
-  }
 #pragma unroll
   for (int d = 16; d; d >>= 1) imax = __vmaxu2(imax, __shfl_xor_sync(0xffffffffu, imax, d));
   if ((t & 31) == 0) warp_max[t >> 5] = imax;
@@ -174,9 +300,9 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
   }
 }
 
-template <int L, bool VEC>
+template <int L, bool VEC, int PRO = kProNone>
 int launch_one(const void* x, int64_t sx, int m, int k, int pm, int pk, int8_t* q, float* sa,
-               cudaStream_t stream) {
+               cudaStream_t stream, const Prologue& pro = Prologue{nullptr, nullptr, 0, 1, 0.f}) {
   constexpr int CV = Chunk<L>::kVec, OW = Chunk<L>::kOutWords, kChunks = kMaxVec / CV;
   const int nvec = (k + 7) / 8;
   const int chunks_in = (nvec + CV - 1) / CV;
@@ -186,7 +312,7 @@ int launch_one(const void* x, int64_t sx, int m, int k, int pm, int pk, int8_t* 
   while (threads * kChunks < chunks) threads <<= 1;
   SS_REQUIRE(threads <= kMaxThreads, SS_E_LIMIT, "front-end: K=%d beyond the supported %d", k,
              kMaxThreads * kMaxVec * 8);
-  quant_lift_kernel<L, VEC><<<pm, threads, 0, stream>>>(static_cast<const uint16_t*>(x), sx, q, sa, m, k, pk, nvec);
+  quant_lift_kernel<L, VEC, PRO><<<pm, threads, 0, stream>>>(static_cast<const uint16_t*>(x), sx, q, sa, m, k, pk, nvec, pro);
   SS_CUDA(cudaGetLastError());
   return SS_OK;
 }
@@ -208,6 +334,40 @@ int launch_quantize_lift(const void* x, int64_t sx, int64_t m, int64_t k, int gr
 #define SS_DISPATCH(LL)                                                                       \
   return vec ? launch_one<LL, true>(x, sx, (int)m, (int)k, (int)pm, (int)pk, q, sa, stream)   \
              : launch_one<LL, false>(x, sx, (int)m, (int)k, (int)pm, (int)pk, q, sa, stream)
+  if (group == 4) { SS_DISPATCH(4); }
+  if (group == 6) { SS_DISPATCH(6); }
+  SS_DISPATCH(8);
+#undef SS_DISPATCH
+}
+
+int launch_quantize_lift_fused(const void* x, int64_t sx, int64_t m, int64_t k, int group, int prologue,
+                               const void* shift, const void* scale, int64_t mod_stride,
+                               int64_t rows_per_batch, float eps, int8_t* q, float* sa, cudaStream_t stream) {
+  if (prologue == kProNone) return launch_quantize_lift(x, sx, m, k, group, q, sa, stream);
+  SS_REQUIRE(prologue == kProNormModulate || prologue == kProGelu, SS_E_ARG, "front-end: unknown prologue %d", prologue);
+  SS_REQUIRE(x && q && sa, SS_E_ARG, "front-end: null pointer");
+  SS_REQUIRE(mode_ok(group), SS_E_ARG, "front-end: group must be 4, 6 or 8 (got %d)", group);
+  SS_REQUIRE(m > 0 && k > 0 && k <= 32768 && m < (1ll << 31) - 32, SS_E_ARG,
+             "front-end: invalid shape m=%lld k=%lld", (long long)m, (long long)k);
+  SS_REQUIRE(sx >= k, SS_E_ARG, "front-end: row stride %lld smaller than k=%lld", (long long)sx, (long long)k);
+  SS_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15) == 0, SS_E_ARG, "front-end: q must be 16-byte aligned");
+  SS_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (sx % 8) == 0 && (k % 8) == 0, SS_E_ARG,
+             "front-end: a prologue needs 16-byte aligned rows and k %% 8 == 0");
+  Prologue pro{static_cast<const uint16_t*>(shift), static_cast<const uint16_t*>(scale), mod_stride,
+               static_cast<int>(rows_per_batch), eps};
+  if (prologue == kProNormModulate) {
+    SS_REQUIRE(shift && scale && rows_per_batch > 0 && rows_per_batch < (1ll << 31) && eps >= 0.f, SS_E_ARG,
+               "front-end: norm+modulate needs shift, scale, rows_per_batch > 0 and eps >= 0");
+    SS_REQUIRE(((reinterpret_cast<uintptr_t>(shift) | reinterpret_cast<uintptr_t>(scale)) & 15) == 0 &&
+                   mod_stride >= k && mod_stride % 8 == 0, SS_E_ARG,
+               "front-end: shift and scale rows must be 16-byte aligned (row stride >= k, multiple of 8)");
+  }
+  const int64_t valid = (k + group - 1) / group * (group / 2 - 1) * 4;
+  const int64_t pk = ceil_to(valid, 128), pm = ceil_to(m, 32);
+#define SS_DISPATCH(LL)                                                                                   \
+  return prologue == kProGelu                                                                             \
+             ? launch_one<LL, true, kProGelu>(x, sx, (int)m, (int)k, (int)pm, (int)pk, q, sa, stream, pro) \
+             : launch_one<LL, true, kProNormModulate>(x, sx, (int)m, (int)k, (int)pm, (int)pk, q, sa, stream, pro)
   if (group == 4) { SS_DISPATCH(4); }
   if (group == 6) { SS_DISPATCH(6); }
   SS_DISPATCH(8);

@@ -16,6 +16,7 @@ import torch
 from torch import nn
 from torch.nn import functional as F
 
+from .backend import Prologue
 from .routing import ProjectionState, OrdinaryProxy, pack_members
 
 
@@ -84,8 +85,15 @@ def grid_embedding(grid, dim):
     return torch.cat([sincos_embedding(ys.reshape(-1), dim // 2), sincos_embedding(xs.reshape(-1), dim // 2)], dim=-1)
 
 
-def modulate(x, shift, scale):
-    return torch.addcmul(shift, x, 1 + scale)
+def gate(x, g, y):
+    """x + g[b] * y with g BF16 [batch, hidden]."""
+    return torch.addcmul(x, g[:, None], y)
+
+
+def norm_modulate(shift, scale):
+    """LayerNorm (no affine, eps 1e-6) followed by x * (1 + scale[b]) + shift[b], as a prologue of
+    the projection that consumes it; shift / scale are BF16 [batch, hidden] (views are fine)."""
+    return Prologue.norm_modulate(shift, scale, 1e-6)
 
 
 class TimestepEmbedder(nn.Module):
@@ -120,11 +128,11 @@ class RoutedAttention(nn.Module):
     def heads_view(self, x):
         return x.reshape(x.shape[0], x.shape[1], self.heads, -1).transpose(1, 2)
 
-    def qkv(self, x, context=None):
+    def qkv(self, x, context=None, prologue=None):
         if self.cross:
-            (q,), (k, v) = self.states[0].members_output(x), self.states[1].members_output(context)
+            (q,), (k, v) = self.states[0].members_output(x, prologue), self.states[1].members_output(context)
         else:
-            q, k, v = self.states[0].members_output(x)
+            q, k, v = self.states[0].members_output(x, prologue)
         q, k, v = self.heads_view(q), self.heads_view(k), self.heads_view(v)
         if self.norm_q is not None:
             q, k = self.norm_q(q), self.norm_k(k)
@@ -134,8 +142,8 @@ class RoutedAttention(nn.Module):
         merged = attended.transpose(1, 2).reshape(attended.shape[0], attended.shape[2], -1)
         return merged if self.to_out is None else self.to_out(merged)
 
-    def forward(self, x, context=None):
-        q, k, v = self.qkv(x, context)
+    def forward(self, x, context=None, prologue=None):
+        q, k, v = self.qkv(x, context, prologue)
         return self.finish(F.scaled_dot_product_attention(q, k, v))
 
 
@@ -150,8 +158,9 @@ class RoutedFeedForward(nn.Module):
     def install(self, states):
         self.fc1, self.fc2 = OrdinaryProxy(states[0]), OrdinaryProxy(states[1])
 
-    def forward(self, x):
-        return self.fc2(F.gelu(self.fc1(x), approximate="tanh"))
+    def forward(self, x, prologue=None):
+        # the GELU is the prologue of the second projection
+        return self.fc2(self.fc1(x, prologue), Prologue.gelu())
 
 
 class DiTBlock(nn.Module):
@@ -160,14 +169,13 @@ class DiTBlock(nn.Module):
     def __init__(self, spec):
         super().__init__()
         h = spec.hidden
-        self.norm1, self.norm2 = (nn.LayerNorm(h, elementwise_affine=False, eps=1e-6) for _ in range(2))
         self.attn, self.ff = RoutedAttention(h, spec.heads), RoutedFeedForward(h, spec.mlp)
         self.adaln = nn.Linear(h, 6 * h)
 
     def forward(self, x, c, context=None):
-        s1, c1, g1, s2, c2, g2 = self.adaln(F.silu(c))[:, None].chunk(6, dim=-1)
-        x = torch.addcmul(x, g1, self.attn(modulate(self.norm1(x), s1, c1)))
-        return torch.addcmul(x, g2, self.ff(modulate(self.norm2(x), s2, c2)))
+        s1, c1, g1, s2, c2, g2 = self.adaln(F.silu(c)).chunk(6, dim=-1)
+        x = gate(x, g1, self.attn(x, prologue=norm_modulate(s1, c1)))
+        return gate(x, g2, self.ff(x, norm_modulate(s2, c2)))
 
 
 class PixArtBlock(nn.Module):
@@ -176,17 +184,16 @@ class PixArtBlock(nn.Module):
     def __init__(self, spec):
         super().__init__()
         h = spec.hidden
-        self.norm1, self.norm2 = (nn.LayerNorm(h, elementwise_affine=False, eps=1e-6) for _ in range(2))
         self.attn = RoutedAttention(h, spec.heads)
         self.cross = RoutedAttention(h, spec.heads, cross=True)
         self.ff = RoutedFeedForward(h, spec.mlp)
         self.table = nn.Parameter(torch.randn(6, h) / math.sqrt(h))
 
     def forward(self, x, c6, context):
-        s1, c1, g1, s2, c2, g2 = (self.table[None] + c6.reshape(c6.shape[0], 6, -1)).unsqueeze(2).unbind(1)
-        x = torch.addcmul(x, g1, self.attn(modulate(self.norm1(x), s1, c1)))
+        s1, c1, g1, s2, c2, g2 = (self.table[None] + c6.reshape(c6.shape[0], 6, -1)).unbind(1)
+        x = gate(x, g1, self.attn(x, prologue=norm_modulate(s1, c1)))
         x = x + self.cross(x, context)
-        return torch.addcmul(x, g2, self.ff(modulate(self.norm2(x), s2, c2)))
+        return gate(x, g2, self.ff(x, norm_modulate(s2, c2)))
 
 
 class JointBlock(nn.Module):
@@ -196,7 +203,6 @@ class JointBlock(nn.Module):
         super().__init__()
         h = spec.hidden
         self.last = last
-        self.norm = nn.LayerNorm(h, elementwise_affine=False, eps=1e-6)
         self.attn = RoutedAttention(h, spec.heads, qk_norm=True)
         self.attn_text = RoutedAttention(h, spec.heads, qk_norm=True, out_proj=not last)
         self.ff = RoutedFeedForward(h, spec.mlp)
@@ -206,18 +212,18 @@ class JointBlock(nn.Module):
 
     def forward(self, x, text, c):
         act = F.silu(c)
-        s1, c1, g1, s2, c2, g2 = self.adaln(act)[:, None].chunk(6, dim=-1)
-        mod_text = self.adaln_text(act)[:, None].chunk(2 if self.last else 6, dim=-1)
-        q, k, v = self.attn.qkv(modulate(self.norm(x), s1, c1))
-        tq, tk, tv = self.attn_text.qkv(modulate(self.norm(text), mod_text[0], mod_text[1]))
+        s1, c1, g1, s2, c2, g2 = self.adaln(act).chunk(6, dim=-1)
+        mod_text = self.adaln_text(act).chunk(2 if self.last else 6, dim=-1)
+        q, k, v = self.attn.qkv(x, prologue=norm_modulate(s1, c1))
+        tq, tk, tv = self.attn_text.qkv(text, prologue=norm_modulate(mod_text[0], mod_text[1]))
         joint = F.scaled_dot_product_attention(torch.cat([q, tq], 2), torch.cat([k, tk], 2), torch.cat([v, tv], 2))
         tokens = x.shape[1]
-        x = torch.addcmul(x, g1, self.attn.finish(joint[:, :, :tokens]))
-        x = torch.addcmul(x, g2, self.ff(modulate(self.norm(x), s2, c2)))
+        x = gate(x, g1, self.attn.finish(joint[:, :, :tokens]))
+        x = gate(x, g2, self.ff(x, norm_modulate(s2, c2)))
         if self.last:
             return x, text
-        text = torch.addcmul(text, mod_text[2], self.attn_text.finish(joint[:, :, tokens:]))
-        text = torch.addcmul(text, mod_text[5], self.ff_text(modulate(self.norm(text), mod_text[3], mod_text[4])))
+        text = gate(text, mod_text[2], self.attn_text.finish(joint[:, :, tokens:]))
+        text = gate(text, mod_text[5], self.ff_text(text, norm_modulate(mod_text[3], mod_text[4])))
         return x, text
 
 
@@ -250,7 +256,6 @@ class Denoiser(nn.Module):
             self.blocks = nn.ModuleList(JointBlock(spec, i == spec.blocks - 1) for i in range(spec.blocks))
         else:
             raise ValueError("unknown denoiser family")
-        self.final_norm = nn.LayerNorm(h, elementwise_affine=False, eps=1e-6)
         self.final_adaln = nn.Linear(h, 2 * h)
         self.final = nn.Linear(h, p * p * spec.out_channels)
         self.states, self.units = [], []
@@ -298,6 +303,12 @@ class Denoiser(nn.Module):
         for state in self.states:
             state.select(mode)
 
+    def fuse_neighbours(self, enabled=True):
+        """Run LayerNorm + modulation and GELU inside the sparse front-end kernels (no effect on
+        the dense path, which keeps them as separate PyTorch operators)."""
+        for state in self.states:
+            state.fuse = bool(enabled)
+
     # -- forward -------------------------------------------------------------------------------
 
     def patchify(self, latent):
@@ -327,8 +338,8 @@ class Denoiser(nn.Module):
             c, text = self.time(t, pooled), self.context(text)
             for block in self.blocks:
                 x, text = block(x, text, c)
-        shift, scale = self.final_adaln(F.silu(c))[:, None].chunk(2, dim=-1)
-        return self.unpatchify(self.final(modulate(self.final_norm(x), shift, scale)))
+        shift, scale = self.final_adaln(F.silu(c)).chunk(2, dim=-1)
+        return self.unpatchify(self.final(norm_modulate(shift, scale).torch_reference(x)))
 
 
 # ------------------------------------------------------------------------------------------------

@@ -21,27 +21,43 @@ class ProjectionState:
         if self.protected and len(self.members) != 1:
             raise ValueError("one original mixed output member required")
         self.widths = tuple(m.out_features for m in members)
+        self.fuse = False      # run prologues inside the sparse operator's front-end kernel
 
     def select(self, mode):
         if type(mode) is not int or mode not in (0, 4, 6, 8) or (mode and mode not in self.ops):
             raise ValueError("missing frozen packed execution mode")
         self.active = mode
 
-    def members_output(self, x):
-        """One output per member (dense), or the fused sparse output split by member widths."""
+    def _sparse(self, x, prologue):
+        op = self.ops[self.active]
+        if prologue is None:
+            return op(x)
+        if self.fuse and hasattr(op, "forward_fused"):
+            return op.forward_fused(x, prologue)
+        return op(prologue.torch_reference(x))
+
+    def members_output(self, x, prologue=None):
+        """One output per member (dense), or the fused sparse output split by member widths.
+        `prologue` (backend.Prologue) is an element-wise neighbour applied to x first: separate
+        PyTorch operators on the dense path, inside the front-end kernel on the sparse path when
+        `fuse` is set."""
         if self.active == 0:
+            if prologue is not None:
+                x = prologue.torch_reference(x)
             return tuple(module(x) for module in self.members)
         if self.protected:
             raise ValueError("protected mixed output is not a shared member projection")
-        return self.ops[self.active](x).split(self.widths, dim=-1)
+        return self._sparse(x, prologue).split(self.widths, dim=-1)
 
-    def output(self, x):
+    def output(self, x, prologue=None):
         """Single-member projection; with a protected prefix the first columns of x stay a BF16
         dense product that the sparse operator adds in its epilogue."""
         if self.active == 0:
-            return self.members[0](x)
+            return self.members[0](x if prologue is None else prologue.torch_reference(x))
         if not self.protected:
-            return self.ops[self.active](x)
+            return self._sparse(x, prologue)
+        if prologue is not None:
+            x = prologue.torch_reference(x)
         original = self.members[0]
         attention = F.linear(x[..., :self.protected], original.weight[:, :self.protected], None)
         return self.ops[self.active](x[..., self.protected:], output_addend=attention)
@@ -64,8 +80,8 @@ class OrdinaryProxy(torch.nn.Module):
         self.in_features = self.original.in_features
         self.out_features = self.original.out_features
 
-    def forward(self, x):
-        return self.state.output(x)
+    def forward(self, x, prologue=None):
+        return self.state.output(x, prologue)
 
 
 def pack_members(members, mode, protected_prefix=0):

@@ -159,6 +159,19 @@ class PackedLinear(torch.nn.Module):
         return run(x, self.packed, self.metadata, self.scales, self.bias, self.mode, self.n, config,
                    output_addend)
 
+    def forward_fused(self, x, prologue, output_addend=None):
+        """forward(prologue(x)) with the prologue (backend.Prologue) computed inside the front-end
+        kernel instead of as separate element-wise passes.  An extension of the reference module."""
+        if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != self.k:
+            raise ValueError("BF16 CUDA input with matching last dimension required")
+        if x.numel() == 0:
+            return x.new_empty((*x.shape[:-1], self.n))
+        if output_addend is not None and (output_addend.shape != (*x.shape[:-1], self.n)
+                                          or output_addend.dtype != torch.bfloat16):
+            raise ValueError("output_addend must match BF16 output shape/device")
+        return backend.projection_fused(x, prologue, self.packed, self.metadata, self.scales, self.bias,
+                                        self.mode, self.n, output_addend)
+
     # -- persistence -----------------------------------------------------------------------------
 
     def save(self, path):
