@@ -20,7 +20,7 @@ def test_mode_switching_matches_oracle(sdk, backend, oracle, residency):
     slot = banks.ResidentBankSlot(payloads, DEV, residency=residency)
     ops = slot.operators(k, n)
     x = oracle.make_activation(m, k, seed=9)
-    bias = np.linspace(-1, 1, n).astype(np.float32)
+    bias = payloads[4]["bias"].numpy()
     for mode in (6, 4, 8, 4):
         slot.activate(mode)
         y = ops[mode](x.to(DEV))
@@ -46,7 +46,7 @@ def test_in_place_coefficients_are_seen_by_a_replayed_graph(sdk, backend, oracle
     with torch.cuda.graph(graph):
         y = op(xd)
     qweight, scales = dense[mode]
-    bias = np.linspace(-1, 1, n).astype(np.float32)
+    bias = payloads[mode]["bias"].numpy()
     graph.replay()
     assert np.array_equal(bits(y), oracle.projection(x, qweight, scales, bias, mode)["out_bits"])
     new_scales = (scales * np.float32(1.5)).astype(np.float32)
