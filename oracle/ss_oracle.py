@@ -21,9 +21,10 @@ names the reference file:line it follows (paths inside the SlideSparse-Diffusion
 Pinning: the reference's tests hold no golden vector for this path; the oracle is pinned
 against outputs of the reference's own CPU code run where the reference is mounted
 (slide_weight, pack_cpu, activation_indices/lift_integer, channel_scales/round_signed), stored
-in tests/golden/ by tests/golden/make_golden.py.  The reference's quantise and GEMM kernels are
-SM80-only and cannot run here, so quantize_lift / gemm_int32 / epilogue are pinned only through
-hand-computed cases and algebraic identities (lift(q) @ slide(w).T == q @ w.T).
+in tests/golden/ by tests/golden/make_golden.py.  quantize_lift, the contraction and the
+epilogue are pinned against outputs of the reference's own GPU operators (quantize, run,
+projection), recompiled unmodified for sm_100 and run on a B200 by oracle/ref_gpu.py, stored in
+tests/golden/ref_gpu.npz.
 """
 import numpy as np
 import torch

@@ -107,3 +107,52 @@ def test_b200_metadata_round_trip(oracle, slide_pack):
         hw = oracle.meta_to_b200(raw, pk)
         assert sorted(oracle.b200_meta_index(raw.shape[0], pk).ravel().tolist()) == list(range(hw.size))
         assert np.array_equal(hw[oracle.b200_meta_index(raw.shape[0], pk)], raw)
+
+
+# ---- vectors produced by the reference's own GPU kernels (oracle/ref_gpu.py, run on a B200) ----
+
+def ref_gpu_cases():
+    import hashlib
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ss_ref_gpu", Path(__file__).parent.parent / "oracle" / "ref_gpu.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module, hashlib
+
+
+def test_quantise_lift_matches_reference_gpu_output(oracle, oracle_c):
+    """quantize (and quantize_packed16) of the reference, recompiled and run on a GPU: INT8
+    activations and token scales, including rows of zeros, sub-floor values, Inf and NaN."""
+    module, hashlib = ref_gpu_cases()
+    data = np.load(GOLDEN / "ref_gpu.npz")
+    assert [tuple(int(v) for v in row) for row in data["cases"]] == [tuple(int(v) for v in c) for c in module.CASES]
+    for index, (mode, m, k, n, config, bias, addend) in enumerate(module.CASES):
+        x, *_ = module.case_inputs(oracle, index, mode, m, k, n, bias, addend)
+        x_bits = x.view(__import__("torch").int16).numpy().view(np.uint16)
+        for impl in (oracle, oracle_c):
+            q, sa = impl.quantize_lift(x if impl is oracle else x_bits, mode)
+            assert hashlib.sha256(np.ascontiguousarray(sa).tobytes()).hexdigest() == str(data[f"sa_sha{index}"]), (index, impl.__name__)
+            assert hashlib.sha256(np.ascontiguousarray(q).tobytes()).hexdigest() == str(data[f"q_sha{index}"]), (index, impl.__name__)
+            if f"q{index}" in data:
+                assert np.array_equal(q, data[f"q{index}"]) and np.array_equal(sa, data[f"sa{index}"])
+
+
+def test_projection_matches_reference_gpu_output(oracle, oracle_c):
+    """run / projection of the reference (sparse GEMM + dequantising epilogue, with and without bias
+    and addend): the BF16 output bit for bit, and its CPU packer's bytes on the way."""
+    module, hashlib = ref_gpu_cases()
+    data = np.load(GOLDEN / "ref_gpu.npz")
+    for index, (mode, m, k, n, config, bias, addend) in enumerate(module.CASES):
+        x, qweight, scales, b, a = module.case_inputs(oracle, index, mode, m, k, n, bias, addend)
+        _, pk = oracle.lifted_k(k, mode)
+        packed, raw = oracle.pack(oracle.slide_weight(qweight, mode), pk)
+        pn = packed.shape[0]
+        sm80 = np.empty(pn * pk // 32, dtype=np.uint32)
+        sm80[oracle.sm80_meta_index(pn, pk).ravel()] = raw.ravel()
+        assert hashlib.sha256(packed.tobytes()).hexdigest() == str(data[f"packed_sha{index}"])
+        assert hashlib.sha256(sm80.view(np.int32).tobytes()).hexdigest() == str(data[f"meta_sha{index}"])
+        q, sa = oracle.quantize_lift(x, mode)
+        acc = oracle.gemm_int32(q, oracle.unpack(packed, raw)[:n], m)
+        out = oracle_c.epilogue(acc, sa, scales, b if b.size else None,
+                                None if a is None else a.view(__import__("torch").int16).numpy().view(np.uint16))
+        assert np.array_equal(out, data[f"y{index}"]), index
