@@ -8,8 +8,8 @@
  * file:line (inside the SlideSparse-Diffusion tree) whose algorithm it restates.
  *
  * Pinning status: slide and pack are pinned against the reference's own CPU code through the
- * golden vectors in tests/golden/; quantise, GEMM and epilogue restate GPU-only reference code
- * that cannot run on this hardware and are pinned through hand-computed cases only.
+ * golden vectors in tests/golden/; quantise, GEMM and epilogue are pinned against the outputs of the
+ * reference's own GPU operators, recompiled for sm_100 and run on a B200 (tests/golden/ref_gpu.npz).
  */
 #include <math.h>
 #include <stdint.h>
