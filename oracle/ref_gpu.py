@@ -18,6 +18,11 @@ not sm_80 (dualscale_sm80.cu:294).  All configurations share one epilogue arithm
 
     python oracle/ref_gpu.py build    [--reference /path/to/SlideSparse-Diffusion]     (CPU box)
     python oracle/ref_gpu.py generate --out tests/golden/ref_gpu.npz                   (GPU box)
+    python oracle/ref_gpu.py time                                                      (GPU box)
+
+`time` prints, for a few benchmark shapes, the device time of the reference's quantize and run
+(configurations 14-16 only, see above: small tiles, not the configurations the reference's own
+profiles pick on an A100) -- context for the B200 kernels, not a tuned baseline.
 """
 import argparse
 import hashlib
@@ -123,14 +128,61 @@ def generate(out):
     print(f"wrote {out}: {len(CASES)} cases on {torch.cuda.get_device_name(0)}")
 
 
+def time_reference():
+    import json
+    import torch
+    sys.path.insert(0, str(HERE.parent))
+    from oracle import ss_oracle as oracle
+    torch.ops.load_library(str(TARGET))
+    front, gemm = torch.ops.sdacc_mild_projection_sm80, torch.ops.sdacc_dualscale_sm80
+    dev = torch.device("cuda", 0)
+    rows = []
+    for (mode, m, k, n) in ((4, 4096, 1152, 4608), (6, 1536, 3072, 9216), (8, 1536, 3072, 12288),
+                            (6, 4096, 3072, 9216), (4, 2048, 1152, 3456), (6, 2048, 2432, 9728)):
+        _, pk = oracle.lifted_k(k, mode)
+        pn, pm = -(-n // 32) * 32, -(-m // 32) * 32
+        x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+        packed = torch.randint(-127, 128, (pn, pk // 2), dtype=torch.int8, device=dev)
+        meta = torch.full((pn * pk // 32,), 0x4E4E4E4E, dtype=torch.int32, device=dev)     # a valid index pair per nibble
+        sw, bias = torch.rand(n, device=dev) + 0.5, torch.rand(n, device=dev)
+        q, sa = front.quantize(x, mode)
+        best = None
+        for config in (14, 15, 16):
+            for _ in range(3):
+                gemm.run(q, packed, meta, sa, sw, bias, m, n, config, None)
+            torch.cuda.synchronize()
+            b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            b.record()
+            for _ in range(20):
+                gemm.run(q, packed, meta, sa, sw, bias, m, n, config, None)
+            e.record()
+            torch.cuda.synchronize()
+            us = b.elapsed_time(e) * 1e3 / 20
+            best = (us, config) if best is None or us < best[0] else best
+        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            front.quantize(x, mode)
+        b.record()
+        for _ in range(20):
+            front.quantize(x, mode)
+        e.record()
+        torch.cuda.synchronize()
+        rows.append(dict(mode=f"{mode - 2}:{mode}", m=m, k=k, n=n, run_us=best[0], run_config=best[1],
+                         quantize_us=b.elapsed_time(e) * 1e3 / 20,
+                         logical_tops=2.0 * m * n * k / (best[0] + b.elapsed_time(e) * 1e3 / 20) / 1e6))
+    print(json.dumps({"device": torch.cuda.get_device_name(0), "rows": rows}))
+
+
 if __name__ == "__main__":
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("action", choices=("build", "generate"))
+    parser.add_argument("action", choices=("build", "generate", "time"))
     parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE", "/root/reference"))
     parser.add_argument("--out", default=str(HERE.parent / "tests" / "golden" / "ref_gpu.npz"))
     parser.add_argument("--force", action="store_true")
     args = parser.parse_args()
     if args.action == "build":
         print(build(args.reference, args.force))
+    elif args.action == "time":
+        time_reference()
     else:
         generate(args.out)

@@ -144,3 +144,25 @@ def test_device_weight_grid(backend, oracle):
     s = torch.empty(37, dtype=torch.float32, device=DEV)
     check(backend, backend.library().ss_weight_grid_device(ptr(w.to(DEV)), 37, 301, ptr(q), ptr(s), stream()))
     assert np.array_equal(s.cpu().numpy(), s_ref) and np.array_equal(q.cpu().numpy(), q_ref)
+
+
+def test_kernels_match_reference_gpu_golden(sdk, backend, oracle):
+    """The B200 kernels against outputs of the reference's own GPU operators (recompiled for
+    sm_100 and run on a B200 by oracle/ref_gpu.py; tests/golden/ref_gpu.npz): INT8 activations,
+    token scales and the BF16 projection output, bit for bit."""
+    import importlib.util
+    from pathlib import Path
+    root = Path(__file__).resolve().parent
+    spec = importlib.util.spec_from_file_location("ss_ref_gpu", root.parent / "oracle" / "ref_gpu.py")
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    data = np.load(root / "golden" / "ref_gpu.npz")
+    for index, (mode, m, k, n, config, has_bias, has_addend) in enumerate(ref.CASES):
+        x, qweight, scales, b, a = ref.case_inputs(oracle, index, mode, m, k, n, has_bias, has_addend)
+        q, sa = sdk.quantize_lift(x.to(DEV), mode)
+        if f"q{index}" in data:
+            assert np.array_equal(q.cpu().numpy(), data[f"q{index}"]) and np.array_equal(sa.cpu().numpy(), data[f"sa{index}"])
+        op = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales),
+                                      torch.from_numpy(b) if b.size else None, mode).to(DEV)
+        y = op(x.to(DEV), output_addend=None if a is None else a.to(DEV))
+        assert np.array_equal(bits(y), data[f"y{index}"]), index
