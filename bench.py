@@ -157,6 +157,17 @@ def run_reference(args, rank, world):
     value = total_ops / total_s / 1e12
     sample = (f"modes 4:6+6:8 x 3 FLUX shapes at M=1536 restricted to the first {SAMPLE_TOKENS} token rows "
               f"({total_ops / args.steps / 1e9:.1f} GOP per step); quantise+lift, int32 torch matmul, epilogue")
+    # context only: the reference's own GPU operators, recompiled unmodified for sm_100, on this GPU
+    # (a separate process: that library and this package define the same torch operator namespaces)
+    recompiled = None
+    if (ROOT / "oracle" / "_ref" / "projection_sm100.so").exists():
+        try:
+            out = subprocess.run([sys.executable, str(ROOT / "oracle" / "ref_gpu.py"), "time"], capture_output=True,
+                                 text=True, timeout=300)
+            if out.returncode == 0:
+                recompiled = json.loads(out.stdout.strip().splitlines()[-1])
+        except (subprocess.SubprocessError, ValueError, IndexError):
+            recompiled = None
     print(json.dumps({
         "impl": "reference", "metric": "sparse_w8a8_linear_tops", "value": value, "unit": "TOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -165,6 +176,7 @@ def run_reference(args, rank, world):
         "config": {"workload": "flux_sweep", "modes": ["4:6", "6:8"], "shapes_kn": SHAPES, "tokens": TOKENS},
         "cpu_baseline": {"value": value, "unit": "TOPS", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "reference_gpu_kernels_recompiled_sm100": recompiled,
     }))
 
 
