@@ -78,6 +78,7 @@ struct KernelArgs {
   int tiles_ch, tiles_tok, num_kb;
   uint32_t* status;
   int wide_cp;          // CTA-pair kernel: copy a stage's two metadata blocks with one tcgen05.cp
+  int meta_warp;        // CTA-pair kernel: a dedicated warp issues the metadata copies
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes,
@@ -407,7 +408,7 @@ int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
     const int nt = cand[i];
     const int64_t tiles = tiles_ch2 * ((m + nt - 1) / nt);
     const int64_t rounds = (tiles + pairs - 1) / pairs;
-    const double main = num_kb * (nt == 256 ? 560.0 : 440.0) + 1500.0 + (nt == 256 ? 3000.0 : 0.0);
+    const double main = num_kb * (nt == 256 ? 560.0 : 420.0) + 1500.0 + (nt == 256 ? 3000.0 : 0.0);
     const double epilogue = 38.0 * nt;
     const double cost = static_cast<double>(rounds) * (main > epilogue ? main : epilogue);
     if (best == 0 || cost < best * 0.999) { best = cost; best_nt = nt; }
@@ -458,6 +459,7 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   k.num_kb = static_cast<int>(a.pk / kBlockK);
   k.status = device_status_ptr();
   k.wide_cp = 0;
+  k.meta_warp = 0;
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
   const int64_t tiles = static_cast<int64_t>(k.tiles_ch) * k.tiles_tok;
   const unsigned grid = static_cast<unsigned>(tiles < dev->sms ? tiles : dev->sms);
@@ -524,6 +526,7 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   k.status = device_status_ptr();
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
   { const char* env = std::getenv("SS_WIDE_CP"); k.wide_cp = env ? std::atoi(env) : 1; }
+  { const char* env = std::getenv("SS_META_WARP"); k.meta_warp = env ? std::atoi(env) : (T::kStages >= 4 ? 1 : 0); }
   const int64_t tiles = static_cast<int64_t>((k.tiles_ch + 1) / 2) * k.tiles_tok;
   const int64_t pairs = dev->sms / 2;
   const unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);

@@ -25,7 +25,11 @@
 #endif
 constexpr int kPairEpiWarps = SS_PAIR_EPI_WARPS;       // 2 or 4 warps per TMEM lane quadrant
 constexpr int kPairSub = kPairEpiWarps / 4;            // warps sharing a quadrant take chunks sub, sub+kPairSub, ...
-constexpr int kPairThreads = 64 + 32 * kPairEpiWarps;
+// The last warp can issue the metadata copies (tcgen05.cp) so that the MMA thread, whose
+// cta_group::2 operations cost about 125 cycles each to issue, only issues MMAs and commits
+// (args.meta_warp).  It adds one barrier hop per stage, which pays with four or more pipeline
+// stages (token tiles up to 224: -6 % on 4096x3072->9216) and costs with three (256).
+constexpr int kPairThreads = 64 + 32 * kPairEpiWarps + 32;
 
 template <int NT, int KB>
 struct PairTile {
@@ -87,7 +91,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   uint64_t* bar_empty = bar_full + T::kStages;
   uint64_t* bar_acc_full = bar_empty + T::kStages;
   uint64_t* bar_acc_empty = bar_acc_full + T::kAccBufs;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + T::kAccBufs);
+  uint64_t* bar_meta = bar_acc_empty + T::kAccBufs;            // metadata of a stage is in TMEM (rank 0)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meta + T::kStages);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -95,11 +100,13 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const int tiles_ch2 = (args.tiles_ch + 1) >> 1;            // tiles of 256 channels
   const int num_tiles = tiles_ch2 * args.tiles_tok;
   const int num_st = (args.num_kb + KB - 1) / KB;
+  const bool meta_warp = args.meta_warp != 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T::kStages; ++s) {
       ptx::mbar_init(&bar_full[s], 1);
       ptx::mbar_init(&bar_empty[s], 1);
+      ptx::mbar_init(&bar_meta[s], 1);
     }
     for (int b = 0; b < T::kAccBufs; ++b) {
       ptx::mbar_init(&bar_acc_full[b], 1);
@@ -167,23 +174,28 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           const uint32_t s = consumed % T::kStages, use = consumed / T::kStages;
           const int kb0 = st * KB;
           const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
-          if (!ready && !ptx::mbar_wait(&bar_full[s], use & 1u)) { ok = false; break; }
+          // with a metadata warp the stage is ready when its metadata copy has completed (which
+          // implies that the operands have landed); without one this thread copies it itself
+          uint64_t* bar_ready = meta_warp ? bar_meta : bar_full;
+          if (!ready && !ptx::mbar_wait(&bar_ready[s], use & 1u)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t a_addr = ptx::smem_u32(smem + T::kOffA + s * T::kABytes);
           const uint32_t b_addr = ptx::smem_u32(smem + T::kOffB + s * T::kBBytes);
-          const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
           const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
-          if (KB == 2 && nkb == 2 && args.wide_cp) {
-            // both metadata blocks of the stage in one instruction: block h is the h-th 16-byte
-            // column of a 128 x 32-byte matrix whose columns lie kEBlock bytes apart
-            ptx::tc_cp_128x256b_pair(e_tmem, smem_desc(e_addr, T::kEBlock, 128, 0));
-          } else {
-            for (int h = 0; h < nkb; ++h)
-              ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+          if (!meta_warp) {
+            const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
+            if (KB == 2 && nkb == 2 && args.wide_cp) {
+              // both metadata blocks of the stage in one instruction: block h is the h-th 16-byte
+              // column of a 128 x 32-byte matrix whose columns lie kEBlock bytes apart
+              ptx::tc_cp_128x256b_pair(e_tmem, smem_desc(e_addr, T::kEBlock, 128, 0));
+            } else {
+              for (int h = 0; h < nkb; ++h)
+                ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+            }
           }
           {
             const uint32_t s2 = (consumed + 1) % T::kStages, use2 = (consumed + 1) / T::kStages;
-            ready = mbar_peek(&bar_full[s2], use2 & 1u);
+            ready = mbar_peek(&bar_ready[s2], use2 & 1u);
           }
           for (int j = 0; j < 2 * nkb; ++j) {
             const uint64_t adesc = smem_desc(a_addr + j * 32, 16, a_sbo, a_layout);
@@ -202,6 +214,35 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           release_stage = -1;
         }
         if (ok) ptx::tc_commit_pair(&bar_acc_full[buf], 3);
+      }
+      if (!ok) atomicOr(args.status, kStatusMmaTimeout);
+    }
+  } else if (warp == 2 + kPairEpiWarps) {
+    // ------------------------------------------------------------------ metadata copier (rank 0 only)
+    if (meta_warp && lane == 0 && rank == 0) {
+      uint32_t copied = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        for (int st = 0; st < num_st; ++st, ++copied) {
+          const uint32_t s = copied % T::kStages, use = copied / T::kStages;
+          const int kb0 = st * KB;
+          const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
+          // the stage's previous metadata is no longer read once its MMAs have completed, which
+          // the producer has already waited for before refilling the stage
+          if (!ptx::mbar_wait(&bar_full[s], use & 1u)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
+          const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
+          if (KB == 2 && nkb == 2 && args.wide_cp) {
+            // both metadata blocks of the stage in one instruction: block h is the h-th 16-byte
+            // column of a 128 x 32-byte matrix whose columns lie kEBlock bytes apart
+            ptx::tc_cp_128x256b_pair(e_tmem, smem_desc(e_addr, T::kEBlock, 128, 0));
+          } else {
+            for (int h = 0; h < nkb; ++h)
+              ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+          }
+          ptx::tc_commit_pair(&bar_meta[s], 1);      // arrives (rank 0 only) when the copy has completed
+        }
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
     }
