@@ -346,7 +346,7 @@ int encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* bas
   return SS_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][5] = {}; };
+struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][4] = {}; };
 DeviceInfo* device_info() {
   static std::mutex mu;
   static std::unordered_map<int, DeviceInfo> table;
@@ -562,10 +562,9 @@ int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream
   if (a.addend) return launch_pair_t<NT, KB, kOutBf16Addend>(a, dev, cfg_index, stream);
   // TMA stores need a 16-byte aligned base and row pitch
   const bool tma_ok = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 && a.out_stride % 8 == 0;
-  const char* env = std::getenv("SS_STORE");          // 0 direct, 1 TMA, 2 staged 16-byte stores
+  const char* env = std::getenv("SS_STORE");          // 0 direct stores, 1 TMA stores (default)
   const int store = env ? std::atoi(env) : 1;
   if (tma_ok && store == 1) return launch_pair_t<NT, KB, kOutBf16Tma>(a, dev, cfg_index, stream);
-  if (tma_ok && store == 2) return launch_pair_t<NT, KB, kOutBf16Staged>(a, dev, cfg_index, stream);
   return launch_pair_t<NT, KB, kOutBf16>(a, dev, cfg_index, stream);
 }
 

@@ -73,7 +73,6 @@ enum : int {
   kOutInt32 = 1,       // raw INT32 accumulators, direct stores
   kOutBf16Addend = 2,  // BF16 with an addend, direct stores
   kOutBf16Tma = 3,     // BF16 staged in shared memory and written with TMA tiled stores
-  kOutBf16Staged = 4,  // BF16 transposed through shared memory, 16-byte global stores
 };
 
 template <int NT, int KB, int MODE>
@@ -376,11 +375,12 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     __syncwarp();
     if (!ok && lane == 0) atomicOr(args.status, kStatusEpilogueTimeout);
   } else {
-    // ------------------------------------------------------------------ epilogue (both CTAs)
+    // ------------------------------------------------------------------ epilogue, direct stores
+    // (unaligned output, addend, INT32 dump): lane = channel, 32 token columns per tcgen05.ld
     const int quad = warp & 3;                    // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;             // which of the quadrant's warps: chunks half, half+kPairSub, ...
     float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
-    uint32_t acc_it = 0, store_it = 0;
+    uint32_t acc_it = 0;
     bool ok = true;
     // Scales of a tile are fetched one tile ahead into registers (the loads fly while the
     // previous tile is processed) and parked in shared memory when the tile starts.
@@ -433,62 +433,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       };
       uint32_t r0[32], r1[32];
       auto emit = [&](const uint32_t (&r)[32], int c) {
-        if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16Staged) {
-          // lane = channel: write the 32x32 BF16 tile token-major, then one tiled store per warp
-          uint8_t* stage = smem + T::kOffStore + ((warp - 2) * T::kStoreBufs + (store_it % T::kStoreBufs)) * T::kStoreTile;
-          if constexpr (MODE == kOutBf16Tma) {
-            if (lane == 0) {
-              if constexpr (T::kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
-            }
-          }
-          __syncwarp();
-          const float* sa_c = sa_s + c * 32;
-          __nv_bfloat16* tile_out = reinterpret_cast<__nv_bfloat16*>(stage) + lane;
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 s4 = reinterpret_cast<const float4*>(sa_c)[j4];
-            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              const int j = j4 * 4 + jj;
-              const float y = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[j])), __fmul_rn(sv[jj], sw), bias);
-              tile_out[j * 32] = __float2bfloat16_rn(y);
-            }
-          }
-          if constexpr (MODE == kOutBf16Tma) {
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
-              // beyond the last channel is not issued at all
-              if (ch < args.n) ptx::tma_store_2d(&map_out, stage, ch, tok0 + c * 32);
-              ptx::bulk_commit();
-            }
-          } else {
-            // read the tile back token-major: four lanes cover the 64 bytes (32 channels) of a token
-            __syncwarp();
-            const int ch_base = ch - lane + (lane & 3) * 8;
-            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(args.out);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int row = (lane >> 2) + 8 * i, tok = tok0 + c * 32 + row;
-              const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 64 + (lane & 3) * 16);
-              if (tok < args.m) {
-                __nv_bfloat16* dst = out + static_cast<long long>(tok) * args.out_stride + ch_base;
-                if (ch_base + 8 <= args.n) {
-                  *reinterpret_cast<uint4*>(dst) = v;
-                } else {
-                  const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
-                  for (int t = 0; t < 8; ++t)
-                    if (ch_base + t < args.n) dst[t] = e[t];
-                }
-              }
-            }
-          }
-          ++store_it;
-        } else {
-          store_chunk<INT32_OUT, HAS_ADDEND>(r, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
-        }
+        store_chunk<INT32_OUT, HAS_ADDEND>(r, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
       };
       const int mine = chunks > half ? (chunks - half + kPairSub - 1) / kPairSub : 0;
       if (mine == 0) {
@@ -508,10 +453,6 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           }
         }
       }
-    }
-    if constexpr (MODE == kOutBf16Tma) {
-      if (lane == 0) ptx::bulk_wait_all();
-      __syncwarp();
     }
     if (!ok && lane == 0) atomicOr(args.status, kStatusEpilogueTimeout);
   }
