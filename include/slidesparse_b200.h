@@ -139,13 +139,20 @@ int ss_quantize_lift_fused(const void* x_bf16, int64_t x_row_stride, int64_t m, 
                            int64_t mod_row_stride, int64_t rows_per_batch, float eps,
                            int8_t* q, float* sa, void* stream);
 /* ss_quantize_lift_fused followed by the GEMM.  No counterpart in the reference (see above);
- * the remaining arguments are those of ss_projection. */
+ * the remaining arguments are those of ss_projection, plus an optional gated accumulation, the
+ * other element-wise neighbour of an FFN-out projection: with gate_bf16 != NULL (BF16
+ * [ceil(m / rows_per_batch), n], rows gate_row_stride elements apart) the kernel does not store y
+ * but adds bf16(gate[row / rows_per_batch, c] * y32[row, c]) to out_bf16 in place (y32 = the fp32
+ * value fma(acc, sa*sw, bias) before its BF16 rounding; the addition is a BF16 round-to-nearest
+ * add done by a TMA reduction), i.e. out is the residual stream.  Needs rows_per_batch % 32 == 0,
+ * a 16-byte aligned out and row pitch, and no addend. */
 int ss_projection_fused(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k, int group,
                         int prologue, const void* shift_bf16, const void* scale_bf16,
                         int64_t mod_row_stride, int64_t rows_per_batch, float eps,
                         const int8_t* packed, const int32_t* meta_b200,
                         const float* sw, const float* bias,
                         const void* addend_bf16, int64_t addend_row_stride,
+                        const void* gate_bf16, int64_t gate_row_stride,
                         int64_t n, int64_t pn,
                         int8_t* q_scratch, float* sa_scratch,
                         void* out_bf16, int64_t out_row_stride, void* stream);

@@ -159,3 +159,20 @@ void sso_epilogue(const int32_t* acc, const float* sa, const float* sw, const fl
       out[i * n + j] = f32_to_bf16(y);
     }
 }
+
+/* Gated accumulation of the fused projection (an extension of this build, no reference
+ * counterpart): out = bf16( float(residual) + float( bf16( gate[row / rows_per_batch, j] * y ) ) ),
+ * y = fma(float(acc), sa*sw, bias) in fp32.  Restates the GEMM epilogue's arithmetic plus the
+ * BF16 round-to-nearest add of the TMA reduction. */
+void sso_epilogue_gated(const int32_t* acc, const float* sa, const float* sw, const float* bias,
+                        const uint16_t* gate, int64_t gate_stride, int64_t rows_per_batch,
+                        const uint16_t* residual, int64_t m, int64_t n, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < m; ++i)
+    for (int64_t j = 0; j < n; ++j) {
+      const float scale = sa[i] * sw[j];
+      const float y = fmaf((float)acc[i * n + j], scale, bias ? bias[j] : 0.f);
+      const float z = bf16_to_f32(f32_to_bf16(bf16_to_f32(gate[(i / rows_per_batch) * gate_stride + j]) * y));
+      out[i * n + j] = f32_to_bf16(bf16_to_f32(residual[i * n + j]) + z);
+    }
+}

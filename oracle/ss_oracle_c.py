@@ -112,3 +112,18 @@ def epilogue(acc, sa, sw, bias=None, addend_bits=None):
 
 if __name__ == "__main__":
     print(build(force=True))
+
+
+def epilogue_gated(acc, sa, sw, bias, gate_bits, rows_per_batch, residual_bits):
+    """BF16 bits of residual + bf16(gate[row // rows_per_batch] * fma(float(acc), sa*sw, bias))."""
+    acc = np.ascontiguousarray(acc, dtype=np.int32)
+    m, n = acc.shape
+    sa = np.ascontiguousarray(sa, dtype=np.float32)
+    sw = np.ascontiguousarray(sw, dtype=np.float32)
+    b = None if bias is None or np.size(bias) == 0 else np.ascontiguousarray(bias, dtype=np.float32)
+    gate = np.ascontiguousarray(gate_bits, dtype=np.uint16)
+    residual = np.ascontiguousarray(residual_bits, dtype=np.uint16).reshape(m, n)
+    out = np.empty((m, n), dtype=np.uint16)
+    load().sso_epilogue_gated(_p(acc), _p(sa), _p(sw), _p(b) if b is not None else None, _p(gate), _i64(gate.shape[1]),
+                              _i64(rows_per_batch), _p(residual), _i64(m), _i64(n), _p(out))
+    return out

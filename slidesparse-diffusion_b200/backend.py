@@ -102,7 +102,7 @@ def _declare(lib):
         "ss_projection": [vp, i64, i64, i64, i32, vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, vp],
         "ss_quantize_lift_fused": [vp, i64, i64, i64, i32, i32, vp, vp, i64, i64, c.c_float, vp, vp, vp],
         "ss_projection_fused": [vp, i64, i64, i64, i32, i32, vp, vp, i64, i64, c.c_float,
-                                vp, vp, vp, vp, vp, i64, i64, i64, vp, vp, vp, i64, vp],
+                                vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, vp, vp, vp, i64, vp],
         "ss_projection_static": [vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, i64, vp, i64, vp],
         "ss_plan_create": [vp, vp, vp, vp, i64, i64, i64, i64, i32, vp],
         "ss_plan_run": [i64, vp, i64, vp, vp, vp, i64, vp],
@@ -355,7 +355,7 @@ class Prologue:
     def arguments(self, x, k):
         """(code, shift, scale, row stride of shift/scale, rows_per_batch, eps) for the C entry."""
         if self.kind != "norm_modulate":
-            return PROLOGUES[self.kind], None, None, 0, 1, 0.0
+            return PROLOGUES[self.kind], None, None, 0, (x.shape[1] if x.ndim == 3 else 1), 0.0
         if x.ndim != 3:
             raise ValueError("norm_modulate needs [batch, rows, k] input")
         batch, rows = x.shape[0], x.shape[1]
@@ -398,8 +398,12 @@ def quantize_lift_fused(input, group, prologue):
     return q, sa
 
 
-def projection_fused(input, prologue, packed, metadata, scales, bias, group, n, output_addend=None):
-    """`projection` with the prologue applied to the input inside the front-end kernel."""
+def projection_fused(input, prologue, packed, metadata, scales, bias, group, n, output_addend=None,
+                     gate=None, residual=None):
+    """`projection` with the prologue applied to the input inside the front-end kernel.
+
+    With `gate` (BF16 [batch, n]) and `residual` (BF16 [batch, rows, n], contiguous) the result is
+    accumulated in place: residual += bf16(gate[b] * y), and `residual` is returned."""
     if not input.is_cuda or input.dtype != torch.bfloat16 or input.ndim < 1:
         raise ValueError("BF16 CUDA input required")
     group = group_size(int(group))
@@ -416,13 +420,29 @@ def projection_fused(input, prologue, packed, metadata, scales, bias, group, n, 
     addend = output_addend
     if addend is not None:
         addend = _check_addend(addend.reshape(-1, n), input.device, m, n)
+    gate_stride = 0
+    if gate is not None:
+        if addend is not None or residual is None or input.ndim != 3:
+            raise ValueError("gated accumulation needs [batch, rows, k] input, a residual and no addend")
+        batch, rows = input.shape[0], input.shape[1]
+        if (residual.dtype != torch.bfloat16 or residual.device != input.device or not residual.is_contiguous()
+                or tuple(residual.shape) != (batch, rows, n) or residual.data_ptr() % 16 or n % 8):
+            raise ValueError("residual must be contiguous, 16-byte aligned BF16 [batch, rows, n] with n % 8 == 0")
+        if gate.dtype != torch.bfloat16 or gate.device != input.device or tuple(gate.shape) != (batch, n) or gate.stride(1) != 1:
+            raise ValueError("gate must be BF16 [batch, n] with unit column stride")
+        if rows % 32:
+            raise ValueError("gated accumulation needs rows per batch to be a multiple of 32")
+        gate_stride = gate.stride(0) if batch > 1 else n
+        out = residual
+    else:
+        out = torch.empty((*input.shape[:-1], n), dtype=torch.bfloat16, device=input.device)
     q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
     sa = torch.empty(pm, dtype=torch.float32, device=input.device)
-    out = torch.empty((*input.shape[:-1], n), dtype=torch.bfloat16, device=input.device)
     with torch.cuda.device(input.device):
         check(library().ss_projection_fused(_ptr(flat), flat.stride(0), m, k, group, code, _ptr(shift), _ptr(scale),
                                             mod_stride, rows, eps, _ptr(packed), _ptr(metadata), _ptr(scales), _ptr(bias),
-                                            _ptr(addend), addend.stride(0) if addend is not None else 0, n, pn,
+                                            _ptr(addend), addend.stride(0) if addend is not None else 0,
+                                            _ptr(gate), gate_stride, n, pn,
                                             _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
     return out
 

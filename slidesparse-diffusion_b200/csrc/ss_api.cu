@@ -157,7 +157,8 @@ extern "C" int ss_projection_fused(const void* x, int64_t sx, int64_t m, int64_t
                                    int64_t mod_stride, int64_t rows_per_batch, float eps,
                                    const int8_t* packed,
                                    const int32_t* meta, const float* sw, const float* bias,
-                                   const void* addend, int64_t addend_stride, int64_t n, int64_t pn,
+                                   const void* addend, int64_t addend_stride,
+                                   const void* gate, int64_t gate_stride, int64_t n, int64_t pn,
                                    int8_t* q_scratch, float* sa_scratch, void* out,
                                    int64_t out_stride, void* stream) {
   int64_t pm, pk;
@@ -169,6 +170,9 @@ extern "C" int ss_projection_fused(const void* x, int64_t sx, int64_t m, int64_t
   GemmArgs a{q_scratch, packed, meta, sa_scratch, sw, bias, addend, addend_stride, out,
              out_stride, m, n, pm, pn, pk, false};
   a.overlap_prologue = true;
+  a.gate = gate;
+  a.gate_stride = gate_stride;
+  a.rows_per_batch = rows_per_batch;
   return launch_gemm(a, s);
 }
 

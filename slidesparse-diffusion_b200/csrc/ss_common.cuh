@@ -62,6 +62,11 @@ struct GemmArgs {
   // kernel may start (set-up, weight prefetch) before that grid has finished and waits on the
   // device before it touches q, sa or out
   bool overlap_prologue = false;
+  // gated accumulation (an extension): out[t, c] += bf16(gate[t / rows_per_batch, c] * y[t, c])
+  // instead of out[t, c] = bf16(y[t, c]); gate is BF16 with gate_stride elements between batches
+  const void* gate = nullptr;
+  int64_t gate_stride = 0;
+  int64_t rows_per_batch = 0;
 };
 struct GemmResources {
   int threads, smem, regs, local, ctas_per_sm, token_tile, stages, tmem_cols;
@@ -237,6 +242,12 @@ __device__ __forceinline__ void tc_wait_ld() {
 }
 
 // TMA tiled store of a shared-memory tile (bulk async-group completion, issuing thread only).
+// TMA tiled reduction: global[tile] += shared[tile], element-wise in the tensor map's type.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)

@@ -79,6 +79,9 @@ struct KernelArgs {
   uint32_t* status;
   int wide_cp;          // CTA-pair kernel: copy a stage's two metadata blocks with one tcgen05.cp
   int meta_warp;        // CTA-pair kernel: a dedicated warp issues the metadata copies
+  const __nv_bfloat16* gate;   // gated accumulation: BF16 [batches, n], rows gate_stride apart
+  long long gate_stride;
+  int rows_per_batch;
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes,
@@ -346,7 +349,7 @@ int encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* bas
   return SS_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][4] = {}; };
+struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][5] = {}; };
 DeviceInfo* device_info() {
   static std::mutex mu;
   static std::unordered_map<int, DeviceInfo> table;
@@ -460,6 +463,7 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   k.status = device_status_ptr();
   k.wide_cp = 0;
   k.meta_warp = 0;
+  k.gate = nullptr; k.gate_stride = 0; k.rows_per_batch = 0;
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
   const int64_t tiles = static_cast<int64_t>(k.tiles_ch) * k.tiles_tok;
   const unsigned grid = static_cast<unsigned>(tiles < dev->sms ? tiles : dev->sms);
@@ -525,12 +529,15 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   k.num_kb = static_cast<int>(a.pk / kBlockK);
   k.status = device_status_ptr();
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
+  k.gate = static_cast<const __nv_bfloat16*>(a.gate);
+  k.gate_stride = a.gate_stride;
+  k.rows_per_batch = static_cast<int>(a.rows_per_batch);
   { const char* env = std::getenv("SS_WIDE_CP"); k.wide_cp = env ? std::atoi(env) : 1; }
   { const char* env = std::getenv("SS_META_WARP"); k.meta_warp = env ? std::atoi(env) : (T::kStages >= 4 ? 1 : 0); }
   const int64_t tiles = static_cast<int64_t>((k.tiles_ch + 1) / 2) * k.tiles_tok;
   const int64_t pairs = dev->sms / 2;
   const unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);
-  if constexpr (MODE == kOutBf16Tma) {
+  if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) {
     // out[m, n] BF16, row pitch out_stride: one 32-channel x 32-token box per epilogue warp and chunk
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.out_stride) * 2};
@@ -562,6 +569,10 @@ int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream
   if (a.addend) return launch_pair_t<NT, KB, kOutBf16Addend>(a, dev, cfg_index, stream);
   // TMA stores need a 16-byte aligned base and row pitch
   const bool tma_ok = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 && a.out_stride % 8 == 0;
+  if (a.gate) {
+    SS_REQUIRE(tma_ok, SS_E_ARG, "gated accumulation needs a 16-byte aligned output and row pitch");
+    return launch_pair_t<NT, KB, kOutBf16GateAdd>(a, dev, cfg_index, stream);
+  }
   const char* env = std::getenv("SS_STORE");          // 0 direct stores, 1 TMA stores (default)
   const int store = env ? std::atoi(env) : 1;
   if (tma_ok && store == 1) return launch_pair_t<NT, KB, kOutBf16Tma>(a, dev, cfg_index, stream);
@@ -591,6 +602,13 @@ int check_args(const GemmArgs& a) {
   SS_REQUIRE(a.int32_out || (reinterpret_cast<uintptr_t>(a.sa) & 15) == 0, SS_E_ARG,
              "gemm: token scales must be 16-byte aligned");
   SS_REQUIRE(!a.addend || a.addend_stride >= a.n, SS_E_ARG, "gemm: addend row stride smaller than n");
+  if (a.gate) {
+    SS_REQUIRE(!a.int32_out && !a.addend, SS_E_ARG, "gemm: gated accumulation excludes the addend and the INT32 dump");
+    SS_REQUIRE(a.rows_per_batch > 0 && a.rows_per_batch % 32 == 0 && a.rows_per_batch < (1ll << 31), SS_E_ARG,
+               "gemm: gated accumulation needs rows_per_batch to be a positive multiple of 32 (got %lld)",
+               (long long)a.rows_per_batch);
+    SS_REQUIRE(a.gate_stride >= a.n, SS_E_ARG, "gemm: gate row stride smaller than n");
+  }
   return SS_OK;
 }
 
@@ -611,6 +629,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
       default:  return launch_pair_nt<256, 2>(a, dev, 3, stream);
     }
   }
+  SS_REQUIRE(!a.gate, SS_E_ARG, "gemm: gated accumulation is implemented by the CTA-pair kernel only");
   const int nt = pick_token_tile(a.m, a.pn, a.pk, dev->sms);
   switch (nt) {
     case 256: return stage_blocks(nt) == 2 ? launch_nt<256, 2>(a, dev, 4, stream) : launch_nt<256, 1>(a, dev, 0, stream);

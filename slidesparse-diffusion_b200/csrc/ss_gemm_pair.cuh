@@ -73,6 +73,7 @@ enum : int {
   kOutInt32 = 1,       // raw INT32 accumulators, direct stores
   kOutBf16Addend = 2,  // BF16 with an addend, direct stores
   kOutBf16Tma = 3,     // BF16 staged in shared memory and written with TMA tiled stores
+  kOutBf16GateAdd = 4, // as kOutBf16Tma, but out += bf16(gate[batch, channel] * y) by TMA reduction
 };
 
 template <int NT, int KB, int MODE>
@@ -115,7 +116,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
     ptx::prefetch_tensormap(&map_e);
-    if constexpr (MODE == kOutBf16Tma) ptx::prefetch_tensormap(&map_out);
+    if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) ptx::prefetch_tensormap(&map_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -245,8 +246,9 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
     }
-  } else if constexpr (MODE == kOutBf16Tma) {
+  } else if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) {
     // ------------------------------------------------------------------ epilogue, TMA stores
+    constexpr bool GATED = MODE == kOutBf16GateAdd;
     // The accumulator is channel-major in TMEM (lane = channel, column = token) and the output is
     // token-major.  tcgen05.ld in the 16x256b fragment layout hands each thread two adjacent
     // tokens of one channel per register pair, which is exactly what stmatrix.trans needs to
@@ -311,6 +313,16 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         __syncwarp();
         const float2* sa_c = reinterpret_cast<const float2*>(sa_s + c * 32 + tpair);
+        // gated accumulation: the 32 tokens of a chunk belong to one batch (rows_per_batch % 32 == 0)
+        float gate[4] = {1.f, 1.f, 1.f, 1.f};
+        if constexpr (GATED) {
+          const __nv_bfloat16* g = args.gate + static_cast<long long>((tok0 + c * 32) / args.rows_per_batch) * args.gate_stride;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int ch = ch_w + lane_ch + 8 * i;
+            gate[i] = ch < args.n ? __bfloat162float(g[ch]) : 0.f;
+          }
+        }
         // this thread addresses row lane%8 of matrix lane/8 in every stmatrix.x4: matrices are
         // (token group, channel group) = (2 gp, 2 h), (2 gp, 2 h + 1), (2 gp + 1, 2 h), (2 gp + 1, 2 h + 1);
         // rows are 64 bytes (32 channels) with the 16-byte pieces XOR-swizzled as TMA's 64B mode expects
@@ -329,8 +341,12 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
               for (int ab = 0; ab < 2; ++ab) {
                 const float w = sw[2 * h + ab], b = bias[2 * h + ab];
-                const float y0 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab])), __fmul_rn(s.x, w), b);
-                const float y1 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab + 1])), __fmul_rn(s.y, w), b);
+                float y0 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab])), __fmul_rn(s.x, w), b);
+                float y1 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab + 1])), __fmul_rn(s.y, w), b);
+                if constexpr (GATED) {
+                  y0 = __fmul_rn(gate[2 * h + ab], y0);
+                  y1 = __fmul_rn(gate[2 * h + ab], y1);
+                }
                 const __nv_bfloat162 p = __floats2bfloat162_rn(y0, y1);     // low half = even token
                 packed[2 * gi + ab] = *reinterpret_cast<const uint32_t*>(&p);
               }
@@ -346,7 +362,10 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) {
           // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
           // beyond the last channel is not issued at all
-          if (ch_w < args.n) ptx::tma_store_2d(&map_out, stage, ch_w, tok0 + c * 32);
+          if (ch_w < args.n) {
+            if constexpr (GATED) ptx::tma_reduce_add_2d(&map_out, stage, ch_w, tok0 + c * 32);
+            else ptx::tma_store_2d(&map_out, stage, ch_w, tok0 + c * 32);
+          }
           ptx::bulk_commit();
         }
         ++store_it;

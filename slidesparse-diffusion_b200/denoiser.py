@@ -158,9 +158,10 @@ class RoutedFeedForward(nn.Module):
     def install(self, states):
         self.fc1, self.fc2 = OrdinaryProxy(states[0]), OrdinaryProxy(states[1])
 
-    def forward(self, x, prologue=None):
-        # the GELU is the prologue of the second projection
-        return self.fc2(self.fc1(x, prologue), Prologue.gelu())
+    def forward(self, x, prologue=None, gated_residual=None):
+        """fc2(gelu(fc1(prologue(x)))); with gated_residual = (residual, gate) the block's
+        residual + gate * (...) is part of the second projection.  The GELU is its prologue."""
+        return self.fc2(self.fc1(x, prologue), Prologue.gelu(), gated_residual)
 
 
 class DiTBlock(nn.Module):
@@ -175,7 +176,7 @@ class DiTBlock(nn.Module):
     def forward(self, x, c, context=None):
         s1, c1, g1, s2, c2, g2 = self.adaln(F.silu(c)).chunk(6, dim=-1)
         x = gate(x, g1, self.attn(x, prologue=norm_modulate(s1, c1)))
-        return gate(x, g2, self.ff(x, norm_modulate(s2, c2)))
+        return self.ff(x, norm_modulate(s2, c2), gated_residual=(x, g2))
 
 
 class PixArtBlock(nn.Module):
@@ -193,7 +194,7 @@ class PixArtBlock(nn.Module):
         s1, c1, g1, s2, c2, g2 = (self.table[None] + c6.reshape(c6.shape[0], 6, -1)).unbind(1)
         x = gate(x, g1, self.attn(x, prologue=norm_modulate(s1, c1)))
         x = x + self.cross(x, context)
-        return gate(x, g2, self.ff(x, norm_modulate(s2, c2)))
+        return self.ff(x, norm_modulate(s2, c2), gated_residual=(x, g2))
 
 
 class JointBlock(nn.Module):
@@ -219,11 +220,11 @@ class JointBlock(nn.Module):
         joint = F.scaled_dot_product_attention(torch.cat([q, tq], 2), torch.cat([k, tk], 2), torch.cat([v, tv], 2))
         tokens = x.shape[1]
         x = gate(x, g1, self.attn.finish(joint[:, :, :tokens]))
-        x = gate(x, g2, self.ff(x, norm_modulate(s2, c2)))
+        x = self.ff(x, norm_modulate(s2, c2), gated_residual=(x, g2))
         if self.last:
             return x, text
         text = gate(text, mod_text[2], self.attn_text.finish(joint[:, :, tokens:]))
-        text = gate(text, mod_text[5], self.ff_text(text, norm_modulate(mod_text[3], mod_text[4])))
+        text = self.ff_text(text, norm_modulate(mod_text[3], mod_text[4]), gated_residual=(text, mod_text[5]))
         return x, text
 
 

@@ -49,9 +49,20 @@ class ProjectionState:
             raise ValueError("protected mixed output is not a shared member projection")
         return self._sparse(x, prologue).split(self.widths, dim=-1)
 
-    def output(self, x, prologue=None):
+    def output(self, x, prologue=None, gated_residual=None):
         """Single-member projection; with a protected prefix the first columns of x stay a BF16
-        dense product that the sparse operator adds in its epilogue."""
+        dense product that the sparse operator adds in its epilogue.  `gated_residual` =
+        (residual [batch, rows, n], gate [batch, n]) asks for residual + gate[b] * y: a PyTorch
+        addcmul on the dense path, an in-place accumulation in the GEMM epilogue on the fused
+        sparse path (rows per batch must then be a multiple of 32)."""
+        if gated_residual is not None:
+            residual, gate = gated_residual
+            op = self.ops.get(self.active)
+            fusable = (self.active != 0 and self.fuse and not self.protected and hasattr(op, "forward_fused")
+                       and x.ndim == 3 and x.shape[1] % 32 == 0 and residual.is_contiguous())
+            if fusable:
+                return op.forward_fused(x, prologue, gate=gate, residual=residual)
+            return torch.addcmul(residual, gate[:, None], self.output(x, prologue))
         if self.active == 0:
             return self.members[0](x if prologue is None else prologue.torch_reference(x))
         if not self.protected:
@@ -80,8 +91,8 @@ class OrdinaryProxy(torch.nn.Module):
         self.in_features = self.original.in_features
         self.out_features = self.original.out_features
 
-    def forward(self, x, prologue=None):
-        return self.state.output(x, prologue)
+    def forward(self, x, prologue=None, gated_residual=None):
+        return self.state.output(x, prologue, gated_residual)
 
 
 def pack_members(members, mode, protected_prefix=0):

@@ -159,18 +159,20 @@ class PackedLinear(torch.nn.Module):
         return run(x, self.packed, self.metadata, self.scales, self.bias, self.mode, self.n, config,
                    output_addend)
 
-    def forward_fused(self, x, prologue, output_addend=None):
-        """forward(prologue(x)) with the prologue (backend.Prologue) computed inside the front-end
-        kernel instead of as separate element-wise passes.  An extension of the reference module."""
+    def forward_fused(self, x, prologue=None, output_addend=None, gate=None, residual=None):
+        """forward(prologue(x)) with the element-wise neighbours inside the kernels: `prologue`
+        (backend.Prologue: LayerNorm + modulation or GELU) is computed by the front-end, and with
+        `gate` [batch, n] and `residual` [batch, rows, n] the epilogue accumulates
+        residual += gate[b] * y in place and returns `residual`.  An extension of the reference module."""
         if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != self.k:
             raise ValueError("BF16 CUDA input with matching last dimension required")
         if x.numel() == 0:
-            return x.new_empty((*x.shape[:-1], self.n))
+            return residual if gate is not None else x.new_empty((*x.shape[:-1], self.n))
         if output_addend is not None and (output_addend.shape != (*x.shape[:-1], self.n)
                                           or output_addend.dtype != torch.bfloat16):
             raise ValueError("output_addend must match BF16 output shape/device")
-        return backend.projection_fused(x, prologue, self.packed, self.metadata, self.scales, self.bias,
-                                        self.mode, self.n, output_addend)
+        return backend.projection_fused(x, prologue or backend.Prologue("none"), self.packed, self.metadata,
+                                        self.scales, self.bias, self.mode, self.n, output_addend, gate, residual)
 
     # -- persistence -----------------------------------------------------------------------------
 

@@ -112,3 +112,44 @@ def test_denoiser_with_fused_neighbours_tracks_unfused(sdk, backend, name):
         fused = model(latent, t, cond).float()
     err = (plain - fused).abs().max() / plain.abs().max().clamp_min(1e-6)
     assert torch.isfinite(fused).all() and float(err) < 0.05, float(err)
+
+
+@pytest.mark.parametrize("mode,k,n,batch,rows", [(4, 512, 200, 2, 64), (6, 1152, 1152, 2, 96), (8, 256, 72, 3, 32)])
+def test_gated_accumulation_matches_oracle(sdk, backend, oracle, oracle_c, mode, k, n, batch, rows):
+    """residual += bf16(gate[b] * y) in the GEMM epilogue (TMA reduction) against the C restatement,
+    bit for bit, with the GELU prologue's activation taken from the GPU front-end itself."""
+    qweight, scales = oracle.make_weight(n, k, mode, seed=3)
+    bias = np.linspace(-0.5, 0.5, n).astype(np.float32)
+    op = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales), torch.from_numpy(bias), mode).to(DEV)
+    x = oracle.make_activation(batch * rows, k, seed=8).reshape(batch, rows, k)
+    g = torch.Generator().manual_seed(4)
+    wide = (0.5 * torch.randn(batch, 6 * n, generator=g)).to(torch.bfloat16)
+    gate = wide[:, 2 * n:3 * n]
+    residual = torch.randn(batch, rows, n, generator=g).to(torch.bfloat16)
+    res_d = residual.to(DEV).clone()
+    out = op.forward_fused(x.to(DEV), None, gate=wide.to(DEV)[:, 2 * n:3 * n], residual=res_d)
+    assert out.data_ptr() == res_d.data_ptr()
+    q, sa = oracle.quantize_lift(x.reshape(-1, k), mode)
+    _, pk = oracle.lifted_k(k, mode)
+    acc = oracle.gemm_int32(q, oracle.slide_weight(qweight, mode), batch * rows)
+    expect = oracle_c.epilogue_gated(acc, sa, scales, bias, gate.contiguous().view(torch.int16).numpy().view(np.uint16),
+                                     rows, residual.view(torch.int16).numpy().view(np.uint16))
+    assert np.array_equal(bits(out).reshape(-1, n), expect)
+    # the same through the PyTorch operators, within BF16 rounding of the intermediate
+    eager = torch.addcmul(residual.to(DEV), wide.to(DEV)[:, 2 * n:3 * n][:, None], op(x.to(DEV)))
+    assert float((eager.float() - out.float()).abs().max()) <= 0.02 * float(eager.float().abs().max())
+
+
+def test_gated_accumulation_argument_errors(sdk, backend, oracle):
+    k, n = 128, 64
+    qweight, scales = oracle.make_weight(n, k, 4, seed=1)
+    op = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales), None, 4).to(DEV)
+    x = torch.zeros(2, 40, k, dtype=torch.bfloat16, device=DEV)            # 40 rows per batch: not a multiple of 32
+    gate = torch.zeros(2, n, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        op.forward_fused(x, None, gate=gate, residual=torch.zeros(2, 40, n, dtype=torch.bfloat16, device=DEV))
+    x = torch.zeros(2, 64, k, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ValueError):
+        op.forward_fused(x, None, gate=gate, residual=torch.zeros(2, 64, n + 8, dtype=torch.bfloat16, device=DEV)[..., :n])
+    with pytest.raises(ValueError):
+        op.forward_fused(x, None, gate=gate)
