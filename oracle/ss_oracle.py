@@ -231,9 +231,7 @@ def frontend_threads(k, mode):
     _, pk = lifted_k(k, l)
     nvec = -(-k // 8)
     chunks = max(-(-nvec // cv), -(-(pk // 4) // ow))
-    threads = 32
-    while threads * per_thread < chunks:
-        threads *= 2
+    threads = -(-(-(-chunks // per_thread)) // 32) * 32       # a multiple of 32 that covers the chunks
     return threads, cv, per_thread
 
 

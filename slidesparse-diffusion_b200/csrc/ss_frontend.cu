@@ -117,7 +117,7 @@ __device__ __forceinline__ void lift_chunk(const uint32_t* qw, uint32_t* ow) {
 template <int L, bool VEC, int PRO = kProNone>
 __global__ void __launch_bounds__(kMaxThreads)
 quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict__ q,
-                  float* __restrict__ sa, int m, int k, int pk, int nvec, const Prologue pro) {
+                  float* __restrict__ sa, int m, int k, int pk, int nvec, int nchunks, const Prologue pro) {
   constexpr int CV = Chunk<L>::kVec, OW = Chunk<L>::kOutWords, kChunks = kMaxVec / CV;
   __shared__ uint32_t warp_max[32];
   __shared__ float warp_fmax[32];
@@ -135,6 +135,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
   uint32_t imax = 0;                                   // packed 16-bit max of |x| bit patterns
 #pragma unroll
   for (int i = 0; i < kChunks; ++i) {
+    if (i * T >= nchunks) break;      // no thread of the CTA owns a chunk from here on
 #pragma unroll
     for (int c = 0; c < CV; ++c) {
       const int idx = (t + i * T) * CV + c;
@@ -157,7 +158,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
   }
   if constexpr (PRO == kProGelu) {
 #pragma unroll
-    for (int i = 0; i < kChunks; ++i)
+    for (int i = 0; i < kChunks && i * T < nchunks; ++i)
 #pragma unroll
       for (int c = 0; c < CV; ++c) {
         uint4& w = v[i][c];
@@ -171,7 +172,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
     // mean and variance over the k valid elements (two passes over the registers)
     float part = 0.f;
 #pragma unroll
-    for (int i = 0; i < kChunks; ++i)
+    for (int i = 0; i < kChunks && i * T < nchunks; ++i)
 #pragma unroll
       for (int c = 0; c < CV; ++c) {
         const uint4 w = v[i][c];
@@ -183,7 +184,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
     const float mean = __fdiv_rn(block_sum(part, warp_fmax, t, T), kf);
     part = 0.f;
 #pragma unroll
-    for (int i = 0; i < kChunks; ++i)
+    for (int i = 0; i < kChunks && i * T < nchunks; ++i)
 #pragma unroll
       for (int c = 0; c < CV; ++c) {
         if ((t + i * T) * CV + c < nvec) {
@@ -202,7 +203,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
     const uint4* shift = reinterpret_cast<const uint4*>(pro.shift + brow);
     const uint4* scale = reinterpret_cast<const uint4*>(pro.scale + brow);
 #pragma unroll
-    for (int i = 0; i < kChunks; ++i)
+    for (int i = 0; i < kChunks && i * T < nchunks; ++i)
 #pragma unroll
       for (int c = 0; c < CV; ++c) {
         const int idx = (t + i * T) * CV + c;
@@ -224,7 +225,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
       }
   }
 #pragma unroll
-  for (int i = 0; i < kChunks; ++i)
+  for (int i = 0; i < kChunks && i * T < nchunks; ++i)
 #pragma unroll
     for (int c = 0; c < CV; ++c) {
       const uint4 w = v[i][c];
@@ -250,7 +251,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
     // absolute maximum with fmaxf semantics: NaN operands are ignored, Inf wins
     float a = 0.f;
 #pragma unroll
-    for (int i = 0; i < kChunks; ++i)
+    for (int i = 0; i < kChunks && i * T < nchunks; ++i)
 #pragma unroll
       for (int c = 0; c < CV; ++c) {
         const uint4 w = v[i][c];
@@ -277,6 +278,7 @@ quant_lift_kernel(const uint16_t* __restrict__ x, int64_t sx, int8_t* __restrict
   const int out_vecs = pk >> 4;
 #pragma unroll
   for (int i = 0; i < kChunks; ++i) {
+    if (i * T >= nchunks) break;      // no thread of the CTA owns a chunk from here on
     const int chunk = t + i * T;
     uint32_t qw[CV * 2 + 1], ow[OW];
 #pragma unroll
@@ -308,11 +310,12 @@ int launch_one(const void* x, int64_t sx, int m, int k, int pm, int pk, int8_t* 
   const int chunks_in = (nvec + CV - 1) / CV;
   const int chunks_out = ((pk >> 2) + OW - 1) / OW;     // padding words are written too
   const int chunks = chunks_in > chunks_out ? chunks_in : chunks_out;
-  int threads = 32;
-  while (threads * kChunks < chunks) threads <<= 1;
+  // a multiple of 32 threads such that threads * kChunks covers the chunks; iterations in which
+  // no thread owns a chunk are skipped inside the kernel
+  const int threads = ((chunks + kChunks - 1) / kChunks + 31) / 32 * 32;
   SS_REQUIRE(threads <= kMaxThreads, SS_E_LIMIT, "front-end: K=%d beyond the supported %d", k,
              kMaxThreads * kMaxVec * 8);
-  quant_lift_kernel<L, VEC, PRO><<<pm, threads, 0, stream>>>(static_cast<const uint16_t*>(x), sx, q, sa, m, k, pk, nvec, pro);
+  quant_lift_kernel<L, VEC, PRO><<<pm, threads, 0, stream>>>(static_cast<const uint16_t*>(x), sx, q, sa, m, k, pk, nvec, chunks, pro);
   SS_CUDA(cudaGetLastError());
   return SS_OK;
 }
