@@ -95,3 +95,24 @@ def prepare_for(workload, module, qweight, scales, bias=None, mode="2:4", attent
             raise ValueError("BF16 protected attention weight required")
         return ProtectedFFNOutput(packed, attention_weight)
     return SharedProjection(packed, group["members"]) if len(group["members"]) > 1 else packed
+
+
+def _workload_module(name):
+    """`workloads.<name>` with WORKLOAD and prepare(module, qweight, scales, ...) bound to it, the
+    per-workload entry the reference keeps as one sub-package each
+    (`sdacc/w8a8_slidesparse/workloads/<name>/__init__.py`); created here from the MODELS table."""
+    import sys
+    import types
+    module = types.ModuleType(f"{__name__}.{name}", f"Constructors for the routed projections of the '{name}' workload.")
+
+    def prepare(module_name, qweight, scales, bias=None, mode="2:4", attention_weight=None, execution="default"):
+        return prepare_for(name, module_name, qweight, scales, bias, mode, attention_weight, execution)
+
+    module.WORKLOAD, module.prepare, module.shapes = name, prepare, (lambda: shapes(name))
+    sys.modules[module.__name__] = module
+    return module
+
+
+for _name in MODELS:
+    globals()[_name] = _workload_module(_name)
+del _name
