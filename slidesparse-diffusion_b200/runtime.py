@@ -1,11 +1,16 @@
-"""One quantise+slide launch and one sparse tcgen05 GEMM launch per projection.
+"""`quantize_lift` and the `PackedLinear` module: the Python face of the projection.
 
-Host-side mirror of the reference's `sdacc/w8a8_slidesparse/runtime.py`: `quantize_lift`
-(:72-95) and the `PackedLinear` module (:98-243) keep their names, constructor and method
-signatures, accepted argument values, buffer names, error types and the save/load payload.  The
-reference's Triton front-ends and SM80 tile configurations do not exist here: every `frontend` /
-`config` / `strategy` value the reference accepts is still accepted (callers pass them), but all
-of them execute the same two sm_100a kernels through the `sdacc_*` operators.
+A forward pass is two kernel launches of the native library, the quantise + slide front-end and
+the sparse tcgen05 GEMM with its dequantising epilogue, reached through the `sdacc_*` torch
+operators that `backend` registers.
+
+The names, constructor and method signatures, accepted argument values, buffer names, exception
+types and the save / load payload keys are those of the reference's
+`sdacc/w8a8_slidesparse/runtime.py` (`quantize_lift` :72-95, `PackedLinear` :98-243), because its
+callers construct the module directly, alias its buffers and pass its SM80 execution choices.
+Those choices (`config` tile ids, `strategy`, Triton / native `frontend` names) select nothing
+here, there is one pair of kernels, but they are validated the same way, and the `graph*` /
+`direct2_*` front-ends still mean "use a prepared plan".
 """
 import hashlib
 from pathlib import Path
@@ -16,191 +21,243 @@ from . import backend
 from .packing import group_size, lifted_k, slide_weight
 from .profile import execution_profile, known_configurations
 
-FRONTENDS = ("triton", "native", "scalar", "packed16", "graph_native", "graph_packed16",
-             "graph1_native", "graph1_packed16", "direct2_native", "direct2_packed16", "auto")
+# values a caller may pass (validated, then mostly ignored: see the module docstring)
 STRATEGIES = ("register", "reload")
-LAYOUT = "b200-v1"     # metadata order tag stored in identity / payloads
+_PLAIN_FRONTENDS = ("triton", "native", "scalar", "packed16")
+_PLAN_FRONTENDS = ("graph_native", "graph_packed16", "graph1_native", "graph1_packed16",
+                   "direct2_native", "direct2_packed16")
+FRONTENDS = _PLAIN_FRONTENDS + _PLAN_FRONTENDS + ("auto",)
+LAYOUT = "b200-v1"          # tag of this library's metadata word order, kept in identity / payloads
+_TENSOR_KEYS = ("packed", "metadata", "scales", "bias")
+_PAYLOAD_VERSION = 1
 
 
 def kernel_source_sha():
+    """Hash of the GEMM source: operators packed for another kernel generation are told apart by it."""
     return backend.sha(Path(__file__).parent / "csrc" / "ss_gemm.cu")
 
 
 def quantize_lift(x, mode="2:4", strategy="register"):
-    """Dynamic per-token quantisation; quantise and dequantise share the same scale floor.
+    """Per-token dynamic INT8 quantisation and slide expansion of a BF16 CUDA matrix.
 
-    x: BF16 CUDA [M,K] with unit column stride (row stride may be larger than K).  Returns
-    (q int8 [ceil32(M), ceil128(K')], scale fp32 [ceil32(M)]); padding and the sliding expansion
-    are produced inside the single kernel.
+    x is [M, K] with unit column stride (any row stride).  Returns `(q, scale)`: q INT8
+    [ceil32(M), ceil128(K')] with K' the lifted width of the mode, scale FP32 [ceil32(M)].  Rows
+    beyond M are zero with scale 1.  The same scale (with its floor) is used to dequantise.
     """
-    length = group_size(mode)
     if strategy not in STRATEGIES:
-        raise ValueError("unknown Quant+Lift strategy")
+        raise ValueError(f"strategy must be one of {STRATEGIES}")
     if x.ndim != 2:
-        raise ValueError("[M,K] input required")
-    return torch.ops.sdacc_mild_projection_sm80.quantize(x, length)
+        raise ValueError("quantize_lift takes a 2-D [M, K] tensor")
+    return torch.ops.sdacc_mild_projection_sm80.quantize(x, group_size(mode))
+
+
+def _check_execution(config, strategy, frontend):
+    if config != "auto" and config not in backend.VALID_CONFIGS:
+        raise ValueError(f"config must be 'auto' or one of {sorted(backend.VALID_CONFIGS)}")
+    if strategy not in STRATEGIES:
+        raise ValueError(f"strategy must be one of {STRATEGIES}")
+    if frontend not in FRONTENDS:
+        raise ValueError(f"frontend must be one of {FRONTENDS}")
+
+
+def _channel_vector(values, channels, what, strictly_positive=False, optional=False):
+    """A per-output-channel parameter as contiguous CPU FP32 [channels]; None -> empty if optional."""
+    if values is None:
+        if not optional:
+            raise ValueError(f"{what} required")
+        return torch.empty(0, dtype=torch.float32)
+    vector = values.detach().to("cpu", torch.float32).contiguous()
+    if optional and vector.numel() == 0:
+        return vector
+    bad = tuple(vector.shape) != (channels,) or not bool(torch.isfinite(vector).all())
+    if bad or (strictly_positive and bool((vector <= 0).any())):
+        kind = "finite and positive" if strictly_positive else "finite"
+        raise ValueError(f"{what} must be {kind} with one value per output channel ({channels})")
+    return vector
+
+
+def _is_plan_frontend(frontend):
+    return frontend in _PLAN_FRONTENDS
 
 
 class PackedLinear(torch.nn.Module):
-    """Frozen packed projection, supporting shared-input QKV/KV concatenation.
+    """A prepared sparse W8A8 projection: y[..., n] = x[..., k] . W^T (+ bias) in BF16.
 
-    Prepare with concatenate([q,k,v]) along output channels, using identically ordered
-    scales/bias, and split the output by widths outside this module.  Buffers `packed`,
-    `metadata`, `scales`, `bias` are read by the kernels at launch time, so callers may overwrite
-    their contents in place between calls.
+    Several projections of the same input (Q|K|V, K|V) are prepared as ONE operator from the
+    row-wise concatenation of their weights, scales and biases; the caller cuts the output back
+    into members (`composite.SharedProjection`).  The four buffers `packed`, `metadata`, `scales`
+    and `bias` are handed to the kernels as pointers at every launch, so a caller may overwrite
+    their contents in place (mode banks, per-step affine coefficients) without a new module.
     """
 
     def __init__(self, packed, metadata, scales, bias, k, n, mode, config="auto",
                  strategy="register", identity=None, frontend="auto"):
         super().__init__()
-        self.k, self.n = int(k), int(n)
+        for key, tensor in zip(_TENSOR_KEYS, (packed, metadata, scales, bias)):
+            self.register_buffer(key, tensor)
+        self.in_features = self.k = int(k)
+        self.out_features = self.n = int(n)
         self.mode = group_size(mode)
-        self.config, self.strategy = ("auto" if config == "auto" else int(config)), strategy
+        self.config = config if config == "auto" else int(config)
+        self.strategy = strategy
         self.frontend = frontend
-        self._graphs = {}
-        self.in_features, self.out_features = self.k, self.n
-        self.identity = identity or {}
-        for name, value in (("packed", packed), ("metadata", metadata),
-                            ("scales", scales), ("bias", bias)):
-            self.register_buffer(name, value)
+        self.identity = dict(identity) if identity else {}
+        self._graphs = {}                     # rows M -> prepared-plan handle
+
+    # ---- offline ------------------------------------------------------------------------------
 
     @classmethod
     def prepare(cls, qweight, scales, bias=None, mode="2:4", config="auto",
                 strategy="register", frontend="auto"):
-        """CPU int8 [N,K] (already pruned and quantised) + fp32 scales [N] -> packed operator."""
-        if (config != "auto" and config not in backend.VALID_CONFIGS) or strategy not in STRATEGIES:
-            raise ValueError("unsupported execution configuration")
-        if frontend not in FRONTENDS:
-            raise ValueError("unknown frontend")
-        n, k = qweight.shape
-        scales = scales.detach().cpu().float().contiguous()
-        bias = torch.empty(0, dtype=torch.float32) if bias is None else bias.detach().cpu().float().contiguous()
-        if scales.shape != (n,) or not torch.isfinite(scales).all() or torch.any(scales <= 0):
-            raise ValueError("finite positive per-channel scales required")
-        if bias.numel() and (bias.shape != (n,) or not torch.isfinite(bias).all()):
-            raise ValueError("finite per-channel bias required")
-        lifted = slide_weight(qweight, mode)
-        _, pk = lifted_k(k, mode)
-        packed, metadata = torch.ops.sdacc_dualscale_sm80.pack_cpu(lifted, pk)
-        identity = dict(qweight_sha=hashlib.sha256(qweight.contiguous().numpy().tobytes()).hexdigest(),
-                        k_physical=pk, k_lifted=lifted.shape[1],
-                        kernel_source_sha=kernel_source_sha(), metadata_layout=LAYOUT)
-        return cls(packed, metadata, scales, bias, k, n, mode, config, strategy, identity, frontend)
+        """Pack an already pruned and quantised weight: CPU INT8 [N, K] with FP32 scales [N]
+        (and optionally an FP32 bias [N]) -> operator with CPU buffers (move it with `.to`)."""
+        _check_execution(config, strategy, frontend)
+        channels, width = qweight.shape
+        channel_scales = _channel_vector(scales, channels, "per-channel scales", strictly_positive=True)
+        channel_bias = _channel_vector(bias, channels, "per-channel bias", optional=True)
+        slid = slide_weight(qweight, mode)                       # raises on a structure violation
+        padded_width = lifted_k(width, mode)[1]
+        values, metadata = torch.ops.sdacc_dualscale_sm80.pack_cpu(slid, padded_width)
+        identity = {
+            "qweight_sha": hashlib.sha256(qweight.contiguous().numpy().tobytes()).hexdigest(),
+            "k_lifted": slid.shape[1],
+            "k_physical": padded_width,
+            "metadata_layout": LAYOUT,
+            "kernel_source_sha": kernel_source_sha(),
+        }
+        return cls(values, metadata, channel_scales, channel_bias, width, channels, mode,
+                   config=config, strategy=strategy, identity=identity, frontend=frontend)
 
-    # -- resources / prepared plans ------------------------------------------------------------
+    # ---- execution choices and prepared plans ---------------------------------------------------
 
-    def _uses_plan(self, frontend):
-        return frontend.startswith(("graph", "direct2_"))
-
-    def _prepare_plan(self, m, config, frontend):
-        ops = torch.ops.sdacc_prepared_projection_sm80
-        make = (ops.prepare_direct2 if frontend.startswith("direct2_")
-                else ops.prepare_singlepatch if frontend.startswith("graph1_") else ops.prepare)
-        return make(self.packed, self.metadata, self.scales, self.bias, self.k, m, self.n,
-                    self.mode, config, frontend.endswith("packed16"))
+    def configuration_for(self, m):
+        """(config, frontend) used for M rows: what the constructor fixed, else the profile's."""
+        profile_config, profile_frontend = execution_profile(self.mode, m, self.k, self.n)
+        config = profile_config if self.config == "auto" else self.config
+        frontend = profile_frontend if self.frontend == "auto" else self.frontend
+        return config, frontend
 
     def configure(self, has_addend=False):
-        """Inspect kernel resources before timing (and build plans for profiled plan shapes)."""
-        configs = known_configurations(self.mode, self.k, self.n) if self.config == "auto" else [self.config]
-        resources = {c: torch.ops.sdacc_dualscale_sm80.configure(self.packed, c, has_addend) for c in configs}
-        return resources if self.config == "auto" else resources[self.config]
+        """Kernel resources `[threads, shared memory, registers, local memory, CTAs per SM]` (twice,
+        as the reference reports a base and a full-tile variant): a dict per configuration when
+        `config` is "auto", else the list of the fixed configuration."""
+        query = torch.ops.sdacc_dualscale_sm80.configure
+        if self.config != "auto":
+            return query(self.packed, self.config, has_addend)
+        return {c: query(self.packed, c, has_addend) for c in known_configurations(self.mode, self.k, self.n)}
 
     def configure_for(self, m):
-        """Offline preparation of a shape-specific plan (resident scratch) for M rows."""
+        """Prepare for M rows ahead of time.  Returns the plan handle if the front-end in force is
+        a prepared-plan one (resident scratch in the native library), else None."""
         config, frontend = self.configuration_for(m)
         self.configure()
-        if self._uses_plan(frontend) and m not in self._graphs:
-            self._graphs[m] = self._prepare_plan(m, config, frontend)
-        return self._graphs.get(m)
+        if not _is_plan_frontend(frontend):
+            return None
+        if m not in self._graphs:
+            namespace = torch.ops.sdacc_prepared_projection_sm80
+            if frontend.startswith("direct2_"):
+                create = namespace.prepare_direct2
+            elif frontend.startswith("graph1_"):
+                create = namespace.prepare_singlepatch
+            else:
+                create = namespace.prepare
+            self._graphs[m] = create(self.packed, self.metadata, self.scales, self.bias, self.k, m, self.n,
+                                     self.mode, config, frontend.endswith("packed16"))
+        return self._graphs[m]
 
     def close_graphs(self):
-        for handle in self._graphs.values():
+        """Release every prepared plan (their handles point at this module's current buffers)."""
+        while self._graphs:
+            _, handle = self._graphs.popitem()
             torch.ops.sdacc_prepared_projection_sm80.release(handle)
-        self._graphs.clear()
 
     def _apply(self, fn, recurse=True):
+        # .to() / .cuda() replace the buffers: plans built over the old ones must go first
         if getattr(self, "_graphs", None):
             self.close_graphs()
         return super()._apply(fn, recurse)
 
-    def configuration_for(self, m):
-        """(config, frontend) for M rows: explicit constructor values win over the profile."""
-        config, frontend = execution_profile(self.mode, m, self.k, self.n)
-        if self.config != "auto":
-            config = self.config
-        if self.frontend != "auto":
-            frontend = self.frontend
-        return config, frontend
+    # ---- forward ----------------------------------------------------------------------------------
 
-    # -- forward ---------------------------------------------------------------------------------
+    def _check_input(self, x):
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == self.k):
+            raise ValueError(f"expected a BF16 CUDA tensor whose last dimension is {self.k}")
+
+    def _flat_addend(self, x, output_addend):
+        expected = (*x.shape[:-1], self.n)
+        if (tuple(output_addend.shape) != expected or output_addend.dtype != torch.bfloat16
+                or output_addend.device != x.device):
+            raise ValueError(f"output_addend must be BF16 {expected} on the input's device")
+        flat = output_addend.reshape(-1, self.n)
+        return flat if flat.stride(-1) == 1 else flat.contiguous()
 
     def forward(self, x, output_addend=None):
-        if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != self.k:
-            raise ValueError("BF16 CUDA input with matching last dimension required")
+        """BF16 [..., k] -> new BF16 [..., n]; `output_addend` (BF16 [..., n]) is added in the epilogue."""
+        self._check_input(x)
         rows = x.numel() // self.k if self.k else 0
         if rows == 0:
             return x.new_empty((*x.shape[:-1], self.n))
         config, frontend = self.configuration_for(rows)
-        if output_addend is not None:
-            if (output_addend.shape != (*x.shape[:-1], self.n) or output_addend.dtype != torch.bfloat16
-                    or output_addend.device != x.device):
-                raise ValueError("output_addend must match BF16 output shape/device")
-            output_addend = output_addend.reshape(-1, self.n)
-            if output_addend.stride(-1) != 1:
-                output_addend = output_addend.contiguous()
-        if self._uses_plan(frontend) and output_addend is None:
-            handle = self._graphs.get(rows)
-            if handle is None:
-                raise RuntimeError("configure_for(M) is required before graph forward")
-            return torch.ops.sdacc_prepared_projection_sm80.run(x, handle, self.n)
-        op = torch.ops.sdacc_mild_projection_sm80
-        run = (op.projection_packed16 if frontend == "packed16"
-               else op.projection_scalar if frontend == "scalar" else op.projection)
-        return run(x, self.packed, self.metadata, self.scales, self.bias, self.mode, self.n, config,
-                   output_addend)
+        addend = None if output_addend is None else self._flat_addend(x, output_addend)
+        if addend is None and _is_plan_frontend(frontend):
+            if rows not in self._graphs:
+                raise RuntimeError(f"no prepared plan for {rows} rows: call configure_for({rows}) first")
+            return torch.ops.sdacc_prepared_projection_sm80.run(x, self._graphs[rows], self.n)
+        operators = torch.ops.sdacc_mild_projection_sm80
+        entry = {"packed16": operators.projection_packed16, "scalar": operators.projection_scalar}.get(
+            frontend, operators.projection)
+        return entry(x, self.packed, self.metadata, self.scales, self.bias, self.mode, self.n, config, addend)
 
     def forward_fused(self, x, prologue=None, output_addend=None, gate=None, residual=None):
         """forward(prologue(x)) with the element-wise neighbours inside the kernels: `prologue`
         (backend.Prologue: LayerNorm + modulation or GELU) is computed by the front-end, and with
         `gate` [batch, n] and `residual` [batch, rows, n] the epilogue accumulates
         residual += gate[b] * y in place and returns `residual`.  An extension of the reference module."""
-        if x.dtype != torch.bfloat16 or not x.is_cuda or x.shape[-1] != self.k:
-            raise ValueError("BF16 CUDA input with matching last dimension required")
+        self._check_input(x)
         if x.numel() == 0:
             return residual if gate is not None else x.new_empty((*x.shape[:-1], self.n))
-        if output_addend is not None and (output_addend.shape != (*x.shape[:-1], self.n)
-                                          or output_addend.dtype != torch.bfloat16):
-            raise ValueError("output_addend must match BF16 output shape/device")
+        if output_addend is not None:
+            self._flat_addend(x, output_addend)            # shape / dtype check only
         return backend.projection_fused(x, prologue or backend.Prologue("none"), self.packed, self.metadata,
                                         self.scales, self.bias, self.mode, self.n, output_addend, gate, residual)
 
-    # -- persistence -----------------------------------------------------------------------------
+    # ---- persistence ------------------------------------------------------------------------------
 
     def save(self, path):
-        """Portable tensor payload; no handles, searched plans, or Python pickle."""
-        torch.save(dict(version=1, k=self.k, n=self.n, mode=self.mode, config=self.config,
-                        strategy=self.strategy, identity=self.identity, frontend=self.frontend,
-                        **{name: tensor.detach().cpu() for name, tensor in self.named_buffers()}), path)
+        """Write a tensors-and-scalars payload (no handles, no pickled objects) that `load` and the
+        reference's own `PackedLinear.load` key set understand."""
+        payload = {"version": _PAYLOAD_VERSION, "k": self.k, "n": self.n, "mode": self.mode,
+                   "config": self.config, "strategy": self.strategy, "frontend": self.frontend,
+                   "identity": self.identity}
+        for key in _TENSOR_KEYS:
+            payload[key] = getattr(self, key).detach().cpu()
+        torch.save(payload, path)
 
     @classmethod
     def load(cls, path, device="cpu", optimized=True):
-        """Load a payload written by save().  A payload written by the reference implementation
-        (metadata in its SM80 order, recognised by the missing layout tag) is converted."""
-        blob = torch.load(path, map_location="cpu", weights_only=True)
-        if blob.pop("version") != 1:
-            raise ValueError("unsupported packed payload version")
-        identity = dict(blob["identity"])
-        if identity.get("metadata_layout") != LAYOUT:
+        """Rebuild an operator from a payload.  One written by the reference (no layout tag; its
+        metadata is in the SM80 kernel's word order) is converted to this library's order.  With
+        `optimized` the stored execution choice is kept in the identity and replaced by "auto"."""
+        payload = torch.load(path, map_location="cpu", weights_only=True)
+        if payload.get("version") != _PAYLOAD_VERSION:
+            raise ValueError(f"payload version {payload.get('version')!r} is not supported")
+        identity = dict(payload["identity"])
+        metadata = payload["metadata"]
+        if identity.get("metadata_layout") == LAYOUT:
+            if identity.get("kernel_source_sha") is None:
+                raise ValueError("the payload does not say which kernel source packed it")
+        else:
             from .importer import sm80_metadata_to_b200
-            pn, half = blob["packed"].shape
-            blob["metadata"] = sm80_metadata_to_b200(blob["metadata"], pn, 2 * half)
-            identity.update(metadata_layout=LAYOUT, imported_from=identity.get("kernel_source_sha"),
-                            kernel_source_sha=kernel_source_sha())
-        elif identity.get("kernel_source_sha") is None:
-            raise ValueError("packing/kernel source identity differs")
-        blob["identity"] = identity
+            rows, half_width = payload["packed"].shape
+            metadata = sm80_metadata_to_b200(metadata, rows, 2 * half_width)
+            identity["imported_from"] = identity.get("kernel_source_sha")
+            identity["kernel_source_sha"] = kernel_source_sha()
+            identity["metadata_layout"] = LAYOUT
+        config, frontend = payload["config"], payload.get("frontend", "triton")
         if optimized:
-            blob["identity"] = dict(identity, loaded_execution_original=dict(
-                config=blob["config"], frontend=blob.get("frontend", "triton")))
-            blob["config"], blob["frontend"] = "auto", "auto"
-        return cls(**blob).to(device)
+            identity["loaded_execution_original"] = {"config": config, "frontend": frontend}
+            config = frontend = "auto"
+        module = cls(payload["packed"], metadata, payload["scales"], payload["bias"], payload["k"], payload["n"],
+                     payload["mode"], config=config, strategy=payload["strategy"], identity=identity,
+                     frontend=frontend)
+        return module.to(device)
