@@ -336,7 +336,8 @@ def run_denoise(args, rank, world, local_rank):
             "config": {"workload": args.workload, "mode": f"{mode - 2}:{mode}", "blocks": spec.blocks,
                        "hidden": spec.hidden, "image_tokens": spec.tokens, "text_tokens": spec.text_tokens,
                        "cfg_batch": 2 * args.images, "sampler": spec.sampler, "sampler_steps": spec.steps,
-                       "routed_projections": projections, "parallelism": f"data-parallel images x{world}",
+                       "routed_projections": projections, "sparse_projections": model.sparse_units(mode),
+                       "parallelism": f"data-parallel images x{world}",
                        "l2": "weights per step exceed L2"},
             "clocks": clocks.summary(),
             "dense_bf16": {"ms_before": dense_before, "ms_after": dense_after, "speedup": dense_ms / sparse_ms,
@@ -347,7 +348,7 @@ def run_denoise(args, rank, world, local_rank):
             "pack_seconds": pack_s,
             "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": latent.numel() * 4 // steps,
                     "d2h_bytes_per_step": latent.numel() * 4 // steps},
-            "gpu_launches": 2 * projections * steps,
+            "gpu_launches": 2 * model.sparse_units(mode) * steps,
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -293,16 +293,25 @@ class Denoiser(nn.Module):
                 else:
                     part.states = states
 
-    def pack(self, mode=None, packer=pack_members):
-        """Prune + quantise + pack every routed group for `mode` (default: the spec's)."""
+    def pack(self, mode=None, packer=pack_members, only_profitable=True):
+        """Prune + quantise + pack the routed groups for `mode` (default: the spec's).  With
+        `only_profitable` the groups that `profile.selectable` rejects for their (M, K, N) get no
+        operator and stay dense under `select` (the reference keeps such shapes dense too)."""
+        from .profile import selectable
         mode = self.spec.mode if mode is None else mode
-        for state in self.states:
+        for state, unit in zip(self.states, self.units):
+            if only_profitable and not selectable(mode, unit["m"], unit["k"], unit["n"]):
+                continue
             state.ops[mode] = packer(state.members, mode)
         return mode
 
     def select(self, mode):
+        """Route every group that has an operator for `mode` through it; the others run dense."""
         for state in self.states:
-            state.select(mode)
+            state.select(mode if mode in state.ops else 0)
+
+    def sparse_units(self, mode):
+        return sum(1 for state in self.states if mode in state.ops)
 
     def fuse_neighbours(self, enabled=True):
         """Run LayerNorm + modulation and GELU inside the sparse front-end kernels (no effect on

@@ -15,3 +15,19 @@ def execution_profile(mode, m, k, n):
 
 def known_configurations(mode, k, n):
     return [DEFAULT[0]]
+
+
+def selectable(mode, m, k, n):
+    """Whether the sparse operator is worth using for this shape on a B200.
+
+    The reference marks shapes it keeps dense in its inventory (`workloads/__init__.py:17`,
+    "keep Dense"); here the rule comes from the per-shape measurements against BF16 `F.linear`
+    (bench.py --workload shapes): projections of less than about 8 GOP are launch-latency sized
+    (PixArt cross-KV at 600 text rows: 10.5 us sparse, 6.6 us dense), and square hidden-sized
+    projections with no element-wise neighbour to absorb (cross-attention Q, 1152 -> 1152) pay
+    more for the quantising front-end than the sparse GEMM saves."""
+    if 2.0 * m * n * k < 8e9:
+        return False
+    if k <= 1536 and n <= 1536:
+        return False
+    return True

@@ -42,7 +42,7 @@ def test_routed_forward_equals_dense_forward(mods, name, per_block):
     t = torch.tensor([500.0, 500.0])
     with torch.no_grad():
         dense = model(latent, t, cond)
-        mode = model.pack(packer=dense_operator)
+        mode = model.pack(packer=dense_operator, only_profitable=False)
         assert mode == spec.mode
         model.select(mode)
         routed = model(latent, t, cond)
@@ -152,3 +152,20 @@ def test_images_for_rank(mods):
         parts = [denoiser.images_for_rank(64, r, world) for r in range(world)]
         assert sorted(sum(parts, [])) == list(range(64))
         assert {len(p) for p in parts} == {64 // world}
+
+
+def test_unprofitable_groups_stay_dense(mods, sdk):
+    """pack() skips the shapes profile.selectable rejects; select() leaves them on the dense path."""
+    denoiser, _ = mods
+    from slidesparse_diffusion_b200 import profile
+    assert not profile.selectable(8, 600, 1152, 2304)          # PixArt cross-KV: launch-latency sized
+    assert not profile.selectable(8, 8192, 1152, 1152)         # cross-attention Q: square, no neighbour to absorb
+    assert profile.selectable(4, 2048, 1152, 3456) and profile.selectable(6, 666, 9728, 2432)
+    spec = denoiser.tiny(denoiser.SPECS["pixart-sigma-1024"])
+    kwargs = {f: getattr(spec, f) for f in ("blocks", "hidden", "heads", "mlp", "grid", "text_tokens",
+                                            "text_dim", "pooled_dim", "classes")}
+    model = denoiser.build("pixart-sigma-1024", device="cpu", dtype=torch.float32, **kwargs)
+    mode = model.pack(packer=dense_operator)                   # tiny shapes: nothing is profitable
+    assert model.sparse_units(mode) == 0
+    model.select(mode)
+    assert all(state.active == 0 for state in model.states)

@@ -50,7 +50,7 @@ def test_sparse_denoise_step_tracks_dense_with_pruned_weights(mods, name):
     kwargs = {f: getattr(spec, f) for f in ("blocks", "hidden", "heads", "mlp", "grid", "text_tokens",
                                             "text_dim", "pooled_dim", "classes")}
     model = denoiser.build(name, device=DEV, steps=4, **kwargs)
-    mode = model.pack()
+    mode = model.pack(only_profitable=False)
     loop = denoiser.DenoiseLoop(model, graph=True)
     cond = loop.conditioning(seed=2)
     side = spec.grid * spec.patch

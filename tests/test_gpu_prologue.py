@@ -99,7 +99,7 @@ def test_denoiser_with_fused_neighbours_tracks_unfused(sdk, backend, name):
     kwargs = {f: getattr(spec, f) for f in ("blocks", "hidden", "heads", "mlp", "grid", "text_tokens",
                                             "text_dim", "pooled_dim", "classes")}
     model = denoiser.build(name, device=DEV, steps=4, **kwargs)
-    mode = model.pack()
+    mode = model.pack(only_profitable=False)
     model.select(mode)
     loop = denoiser.DenoiseLoop(model)
     cond = loop.conditioning(seed=2)
