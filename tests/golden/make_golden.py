@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted and oracle/_ref has been built (oracle/build_ref.py):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference /path/to/SlideSparse-Diffusion]
 
 Imports only the reference (never this repository's package: both register the same torch
 operator namespace, so they cannot share a process) and writes small .npz fixtures next to this
