@@ -264,6 +264,31 @@ def run_shapes(args, local_rank):
                       "peaks": pk, "rows": rows}))
 
 
+def run_micro(local_rank):
+    """Tensor-pipe versus shared-memory bound of single-CTA INT8 MMAs (one JSON line)."""
+    import torch
+    from __graft_entry__ import load_package
+    sdk = load_package()
+    sdk.load_native()
+    from slidesparse_diffusion_b200 import backend
+    torch.cuda.set_device(local_rank)
+    torch.zeros(1, device="cuda")                      # creates the context the library launches into
+    rows = []
+    for sparse in (True, False):
+        for nt in (64, 128, 192, 256):
+            cycles = backend.micro_mma_rate(nt, sparse)
+            tensor_cycles = 128.0 * nt * 64 / 16384 if sparse else 128.0 * nt * 32 / 8192
+            operand_bytes = 128 * 32 + nt * (64 if sparse else 32)
+            rows.append({"kind": "sparse i8 K=64" if sparse else "dense i8 K=32", "token_tile": nt,
+                         "cycles_per_mma": cycles, "tensor_pipe_cycles": tensor_cycles,
+                         "pct_of_tensor_peak": 100.0 * tensor_cycles / cycles,
+                         "operand_bytes_per_cycle": operand_bytes / cycles})
+    rows.append({"kind": "sparse i8 K=64 + metadata copy per 2 MMAs", "token_tile": 256,
+                 "cycles_per_mma": backend.micro_mma_rate(256, True, True)})
+    print(json.dumps({"metric": "mma_cycles", "unit": "cycles", "n_gpus": 1, "data": "synthetic", "dtype": "int8",
+                      "config": {"workload": "micro"}, "rows": rows}))
+
+
 def run_denoise(args, rank, world, local_rank):
     """Denoise-step latency: sparse routed projections against dense BF16 on the same model."""
     import torch
@@ -363,7 +388,7 @@ def main():
     parser.add_argument("--tokens", type=str, default=None, help="comma-separated M values (debug)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="flux_sweep",
-                        choices=("flux_sweep", "shapes", "dit-xl-512", "pixart-sigma-1024", "sd35-large-512"))
+                        choices=("flux_sweep", "shapes", "micro", "dit-xl-512", "pixart-sigma-1024", "sd35-large-512"))
     parser.add_argument("--images", type=int, default=1, help="images per forward in the denoise workloads")
     parser.add_argument("--blocks", type=int, default=None, help="override the block count (debug)")
     args = parser.parse_args()
@@ -377,6 +402,10 @@ def main():
     if args.workload == "shapes":
         if rank == 0:
             run_shapes(args, local_rank)
+        return
+    if args.workload == "micro":
+        if rank == 0:
+            run_micro(local_rank)
         return
     if args.workload != "flux_sweep":
         run_denoise(args, rank, world, local_rank)

@@ -157,6 +157,15 @@ int ss_projection_fused(const void* x_bf16, int64_t x_row_stride, int64_t m, int
                         int8_t* q_scratch, float* sa_scratch,
                         void* out_bf16, int64_t out_row_stride, void* stream);
 
+/* Diagnostic.  No counterpart in the reference.  Runs one CTA that issues `iterations` x 2
+ * back-to-back tcgen05.mma instructions of 128 channels x token_tile tokens (sparse kind::i8 with
+ * K = 64 lifted columns, or dense kind::i8 with K = 32) on operands that rotate through shared
+ * memory, optionally with the per-block metadata copy, and returns the cycles per instruction.
+ * Used to show which resource bounds the GEMM main loop (shared-memory operand reads at
+ * 128 B/clk/SM).  Synchronises the device; token_tile in {64, 128, 192, 256}. */
+int ss_micro_mma_rate(int token_tile, int sparse, int with_metadata_copy, int iterations,
+                      double* cycles_per_mma);
+
 /* The complete projection (front-end + GEMM, no addend) for callers that cannot allocate device
  * memory at all: hosts whose HBM is fully carved into their own pools, loops in which
  * cudaMalloc/cudaFree are banned because they lock, block and may fail, plug-ins without access

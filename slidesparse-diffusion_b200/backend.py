@@ -23,7 +23,7 @@ from .packing import group_size, lifted_k
 
 SS_E_ARG, SS_E_CUDA, SS_E_FORMAT, SS_E_HANDLE, SS_E_DEVICE, SS_E_LIMIT = -1, -2, -3, -4, -5, -6
 LIBRARY_NAME = "libslidesparse_b200.so"
-SOURCES = ("ss_api.cu", "ss_gemm.cu", "ss_frontend.cu", "ss_pack.cu", "ss_noalloc.cu")
+SOURCES = ("ss_api.cu", "ss_gemm.cu", "ss_frontend.cu", "ss_pack.cu", "ss_noalloc.cu", "ss_micro.cu")
 ARCH = "sm_100a"
 VALID_CONFIGS = (0, 1, 2, 3, 4, 5, 6, 11, 12, 13, 14, 15, 16, 17)
 
@@ -110,6 +110,7 @@ def _declare(lib):
         "ss_plan_resources": [i64, vp, i32],
         "ss_gemm_resources": [i64, i64, i64, vp, i32],
         "ss_device_status": [vp, vp],
+        "ss_micro_mma_rate": [i32, i32, i32, i32, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -318,6 +319,14 @@ def _projection(input, packed, metadata, scales, bias, group, n, config, output_
                                       addend.stride(0) if addend is not None else 0, n, pn,
                                       _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
     return out
+
+
+def micro_mma_rate(token_tile, sparse=True, with_metadata_copy=False, iterations=512):
+    """Cycles per back-to-back 128 x token_tile INT8 tcgen05.mma of one CTA (diagnostic)."""
+    value = ctypes.c_double()
+    check(library().ss_micro_mma_rate(int(token_tile), int(bool(sparse)), int(bool(with_metadata_copy)),
+                                      int(iterations), ctypes.byref(value)))
+    return value.value
 
 
 PROLOGUES = {"none": 0, "norm_modulate": 1, "gelu": 2}
