@@ -82,6 +82,7 @@ struct KernelArgs {
   const __nv_bfloat16* gate;   // gated accumulation: BF16 [batches, n], rows gate_stride apart
   long long gate_stride;
   int rows_per_batch;
+  int res_stages;       // weights-resident form: activation pipeline stages
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes,
@@ -349,7 +350,7 @@ int encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* bas
   return SS_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][5] = {}; };
+struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][5][2] = {}; };
 DeviceInfo* device_info() {
   static std::mutex mu;
   static std::unordered_map<int, DeviceInfo> table;
@@ -464,6 +465,7 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   k.wide_cp = 0;
   k.meta_warp = 0;
   k.gate = nullptr; k.gate_stride = 0; k.rows_per_batch = 0;
+  k.res_stages = 0;
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
   const int64_t tiles = static_cast<int64_t>(k.tiles_ch) * k.tiles_tok;
   const unsigned grid = static_cast<unsigned>(tiles < dev->sms ? tiles : dev->sms);
@@ -486,13 +488,15 @@ bool pdl_enabled() {
 }
 
 // ---- CTA-pair launcher -----------------------------------------------------------------------
-template <int NT, int KB, int MODE>
-int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
+// RES: weights-resident form (see PairResident); res_stages = its activation pipeline depth.
+template <int NT, int KB, int MODE, bool RES = false>
+int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream, int res_stages = 0) {
   using T = PairTile<NT, KB>;
-  auto kernel = sparse_gemm_pair_kernel<NT, KB, MODE>;
-  if (!dev->pair_configured[cfg_index][MODE]) {
-    SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
-    dev->pair_configured[cfg_index][MODE] = true;
+  auto kernel = sparse_gemm_pair_kernel<NT, KB, MODE, RES>;
+  if (!dev->pair_configured[cfg_index][MODE][RES]) {
+    SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 RES ? 227 * 1024 : T::kSmemBytes));
+    dev->pair_configured[cfg_index][MODE][RES] = true;
   }
   CUtensorMap map_a, map_b, map_e, map_out;
   {
@@ -534,9 +538,20 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   k.rows_per_batch = static_cast<int>(a.rows_per_batch);
   { const char* env = std::getenv("SS_WIDE_CP"); k.wide_cp = env ? std::atoi(env) : 1; }
   { const char* env = std::getenv("SS_META_WARP"); k.meta_warp = env ? std::atoi(env) : (T::kStages >= 4 ? 1 : 0); }
-  const int64_t tiles = static_cast<int64_t>((k.tiles_ch + 1) / 2) * k.tiles_tok;
+  k.res_stages = res_stages;
+  const int64_t tiles_ch2 = (k.tiles_ch + 1) / 2;
+  const int64_t tiles = tiles_ch2 * k.tiles_tok;
   const int64_t pairs = dev->sms / 2;
-  const unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);
+  unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);
+  int smem_bytes = T::kSmemBytes;
+  if constexpr (RES) {
+    // a whole number of clusters per channel tile, so that a cluster never changes its weights
+    int64_t group = pairs / tiles_ch2;
+    if (group > k.tiles_tok) group = k.tiles_tok;
+    SS_REQUIRE(group >= 1 && res_stages >= 3, SS_E_ARG, "gemm: resident form not applicable");
+    grid = 2u * static_cast<unsigned>(group * tiles_ch2);
+    smem_bytes = PairResident<NT, KB>::smem_bytes((k.num_kb + KB - 1) / KB, res_stages);
+  }
   if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) {
     // out[m, n] BF16, row pitch out_stride: one 32-channel x 32-token box per epilogue warp and chunk
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m)};
@@ -551,7 +566,7 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kPairThreads);
-  cfg.dynamicSmemBytes = T::kSmemBytes;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -563,10 +578,37 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   return SS_OK;
 }
 
+// Weights-resident form: applicable when the K extent's metadata fits the TMEM columns left beside
+// two accumulators and there are no more channel tiles than clusters; worth using (measured) only
+// when at least four activation stages fit next to the weights (lifted K up to about 1300: with
+// three the pipeline is too shallow, 6:8 at K = 1152 ran 30 % slower) and a cluster sees at least
+// four token tiles (the weights are fetched before the first MMA; with two tiles that start-up
+// costs more than the re-use saves).  Returns the activation pipeline depth, 0 if not applicable.
+template <int NT>
+int resident_stages(const GemmArgs& a, int sms) {
+  using R = PairResident<NT, 2>;
+  const int64_t num_kb = a.pk / kBlockK, slabs = (num_kb + 1) / 2;
+  const int64_t tiles_ch2 = (a.pn + 2 * kTileCh - 1) / (2 * kTileCh), tiles_tok = (a.m + NT - 1) / NT;
+  const int64_t pairs = sms / 2;
+  if (slabs > R::kMaxStagesK || tiles_ch2 > pairs) return 0;
+  const int stages = R::b_stages(static_cast<int>(slabs));
+  if (stages < 4 || num_kb * R::T::kEBlock > static_cast<int64_t>(stages) * R::T::kBBytes) return 0;
+  const int64_t group = pairs / tiles_ch2;
+  if (tiles_tok < 4 * group) return 0;
+  return stages;
+}
+
 template <int NT, int KB>
-int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream) {
+int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream, int res_stages = 0) {
   if (a.int32_out) return launch_pair_t<NT, KB, kOutInt32>(a, dev, cfg_index, stream);
   if (a.addend) return launch_pair_t<NT, KB, kOutBf16Addend>(a, dev, cfg_index, stream);
+  if constexpr (KB == 2 && NT <= 224) {
+    if (res_stages > 0) {
+      const bool aligned = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 && a.out_stride % 8 == 0;
+      if (aligned && a.gate) return launch_pair_t<NT, KB, kOutBf16GateAdd, true>(a, dev, cfg_index, stream, res_stages);
+      if (aligned) return launch_pair_t<NT, KB, kOutBf16Tma, true>(a, dev, cfg_index, stream, res_stages);
+    }
+  }
   // TMA stores need a 16-byte aligned base and row pitch
   const bool tma_ok = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 && a.out_stride % 8 == 0;
   if (a.gate) {
@@ -622,6 +664,17 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   // comparison and for token tiles of 64).
   const char* pair_env = std::getenv("SS_PAIR");
   if (!pair_env || std::atoi(pair_env) != 0) {
+    // SS_RESIDENT=0 switches the weights-resident form off
+    const char* res_env = std::getenv("SS_RESIDENT");
+    const bool token_tile_forced = std::getenv("SS_TOKEN_TILE") != nullptr;
+    if (!(res_env && std::atoi(res_env) == 0) && !a.int32_out && !a.addend && !token_tile_forced) {
+      // prefer the token tile that needs fewer rounds of the clusters that share a channel tile
+      const int s224 = resident_stages<224>(a, dev->sms), s192 = resident_stages<192>(a, dev->sms);
+      const int64_t tiles_ch2 = (a.pn + 2 * kTileCh - 1) / (2 * kTileCh), group = (dev->sms / 2) / (tiles_ch2 ? tiles_ch2 : 1);
+      auto rounds = [&](int nt) { const int64_t t = (a.m + nt - 1) / nt; return (t + group - 1) / group; };
+      if (s224 && (!s192 || rounds(224) * 224 <= rounds(192) * 192)) return launch_pair_nt<224, 2>(a, dev, 2, stream, s224);
+      if (s192) return launch_pair_nt<192, 2>(a, dev, 1, stream, s192);
+    }
     switch (pick_pair_token_tile(a.m, a.pn, a.pk, dev->sms)) {
       case 128: return launch_pair_nt<128, 2>(a, dev, 0, stream);
       case 192: return launch_pair_nt<192, 2>(a, dev, 1, stream);

@@ -76,7 +76,24 @@ enum : int {
   kOutBf16GateAdd = 4, // as kOutBf16Tma, but out += bf16(gate[batch, channel] * y) by TMA reduction
 };
 
-template <int NT, int KB, int MODE>
+// Shared-memory layout of the weights-resident form (RES): the whole K extent of the CTA's 128
+// weight rows stays in shared memory (one slab per pipeline stage of K), the metadata of the whole
+// K extent stays in TMEM, and the pipeline stages hold activations only.
+template <int NT, int KB>
+struct PairResident {
+  using T = PairTile<NT, KB>;
+  static constexpr int kMaxStagesK = (kTmemCols - 2 * NT) / T::kMetaColsPerStage;   // TMEM left for metadata
+  static constexpr int kFixed = T::kSaBytes + kPairEpiWarps * T::kStoreTile + 256 + 1024;
+  // B pipeline stages that fit next to `slabs` resident A slabs (0 if fewer than 3)
+  static int b_stages(int slabs) {
+    const int room = 227 * 1024 - kFixed - slabs * T::kABytes;
+    const int stages = room / T::kBBytes;
+    return stages < 3 ? 0 : (stages > 8 ? 8 : stages);
+  }
+  static int smem_bytes(int slabs, int stages) { return slabs * T::kABytes + stages * T::kBBytes + kFixed; }
+};
+
+template <int NT, int KB, int MODE, bool RES = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b,
@@ -87,23 +104,41 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + T::kOffBar);
-  uint64_t* bar_empty = bar_full + T::kStages;
-  uint64_t* bar_acc_full = bar_empty + T::kStages;
+  const int num_st = (args.num_kb + KB - 1) / KB;
+  // pipeline depth and region offsets: compile-time in the streaming form, from the K extent in
+  // the resident form (A slabs first, then the B stages, which also stage the metadata once)
+  const int stages = RES ? args.res_stages : T::kStages;
+  const int off_a = 0;
+  const int off_b = RES ? num_st * T::kABytes : T::kOffB;
+  const int off_e = RES ? off_b : T::kOffE;
+  const int off_sa = RES ? off_b + stages * T::kBBytes : T::kOffSa;
+  const int off_store = off_sa + T::kSaBytes;
+  constexpr int kStoreBufs = RES ? 1 : T::kStoreBufs;
+  const int off_bar = off_store + kStoreBufs * kPairEpiWarps * T::kStoreTile;
+  constexpr int kBarStride = RES ? 8 : T::kStages;
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + off_bar);
+  uint64_t* bar_empty = bar_full + kBarStride;
+  uint64_t* bar_acc_full = bar_empty + kBarStride;
   uint64_t* bar_acc_empty = bar_acc_full + T::kAccBufs;
-  uint64_t* bar_meta = bar_acc_empty + T::kAccBufs;            // metadata of a stage is in TMEM (rank 0)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meta + T::kStages);
+  // streaming form: metadata of a stage is in TMEM (rank 0).  Resident form: [0] metadata of the
+  // whole K extent is in TMEM (both CTAs), [1] resident operands have landed (rank 0)
+  uint64_t* bar_meta = bar_acc_empty + T::kAccBufs;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meta + kBarStride);
+  static_assert(!RES || T::kAccBufs == 2, "resident form assumes two accumulators");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int tiles_ch2 = (args.tiles_ch + 1) >> 1;            // tiles of 256 channels
   const int num_tiles = tiles_ch2 * args.tiles_tok;
-  const int num_st = (args.num_kb + KB - 1) / KB;
-  const bool meta_warp = args.meta_warp != 0;
+  const bool meta_warp = !RES && args.meta_warp != 0;
+  // Tile sequence of this cluster: pair, pair + num_pairs, ...; tile = token tile * tiles_ch2 +
+  // channel tile.  The resident form is launched with a cluster count that is a multiple of
+  // tiles_ch2, so every tile of a cluster has the same channel tile (tile % tiles_ch2).
+  const int tile_first = pair, tile_step = num_pairs;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < T::kStages; ++s) {
+    for (int s = 0; s < kBarStride; ++s) {
       ptx::mbar_init(&bar_full[s], 1);
       ptx::mbar_init(&bar_empty[s], 1);
       ptx::mbar_init(&bar_meta[s], 1);
@@ -131,26 +166,45 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
-      uint32_t issued = 0;
+      uint32_t s = 0, phase = 0;       // pipeline stage and the parity of its current use
       bool ok = true;
+      if constexpr (RES) {
+        // the weights do not depend on the preceding kernel: fetch the resident operands first
+        if (tile_first < num_tiles) {
+          const int ch0 = (tile_first % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
+          if (rank == 0)
+            ptx::mbar_arrive_expect_tx(&bar_meta[1], 2 * (num_st * T::kABytes + args.num_kb * T::kEBlock));
+          for (int st = 0; st < num_st; ++st)
+            ptx::tma_load_2d_pair(smem + off_a + st * T::kABytes, &map_a, &bar_meta[1], st * KB * (kBlockK / 2), ch0);
+          for (int kb = 0; kb < args.num_kb; ++kb)
+            ptx::tma_load_3d_pair(smem + off_e + kb * T::kEBlock, &map_e, &bar_meta[1], 0, kb, ch0 >> 5);
+          // the metadata is staged where the first activation stages will live
+          if (!ptx::mbar_wait(&bar_meta[0], 0)) ok = false;
+        }
+      }
       ptx::grid_dep_wait();           // q is written by the kernel launched just before this one
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step) {
         const int ch0 = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
         const int tok0 = (tile / tiles_ch2) * NT + static_cast<int>(rank) * T::kHalf;
-        for (int st = 0; st < num_st; ++st, ++issued) {
-          const uint32_t s = issued % T::kStages, use = issued / T::kStages;
+        for (int st = 0; st < num_st; ++st) {
           const int kb0 = st * KB;
           const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
-          if (!ptx::mbar_wait(&bar_empty[s], (use & 1u) ^ 1u)) { ok = false; break; }
-          if (rank == 0)
-            ptx::mbar_arrive_expect_tx(&bar_full[s], 2 * (T::kABytes + nkb * (T::kBBlock + T::kEBlock)));
-          ptx::tma_load_2d_pair(smem + T::kOffA + s * T::kABytes, &map_a, &bar_full[s], kb0 * (kBlockK / 2), ch0);
-          for (int h = 0; h < nkb; ++h) {
-            ptx::tma_load_2d_pair(smem + T::kOffB + s * T::kBBytes + h * T::kBBlock, &map_b, &bar_full[s],
-                                  (kb0 + h) * kBlockK, tok0);
-            ptx::tma_load_3d_pair(smem + T::kOffE + s * T::kEBytes + h * T::kEBlock, &map_e, &bar_full[s], 0,
-                                  kb0 + h, ch0 >> 5);
+          if (!ptx::mbar_wait(&bar_empty[s], phase ^ 1u)) { ok = false; break; }
+          if constexpr (RES) {
+            if (rank == 0) ptx::mbar_arrive_expect_tx(&bar_full[s], 2 * nkb * T::kBBlock);
+          } else {
+            if (rank == 0)
+              ptx::mbar_arrive_expect_tx(&bar_full[s], 2 * (T::kABytes + nkb * (T::kBBlock + T::kEBlock)));
+            ptx::tma_load_2d_pair(smem + off_a + s * T::kABytes, &map_a, &bar_full[s], kb0 * (kBlockK / 2), ch0);
           }
+          for (int h = 0; h < nkb; ++h) {
+            ptx::tma_load_2d_pair(smem + off_b + s * T::kBBytes + h * T::kBBlock, &map_b, &bar_full[s],
+                                  (kb0 + h) * kBlockK, tok0);
+            if constexpr (!RES)
+              ptx::tma_load_3d_pair(smem + off_e + s * T::kEBytes + h * T::kEBlock, &map_e, &bar_full[s], 0,
+                                    kb0 + h, ch0 >> 5);
+          }
+          if (++s == static_cast<uint32_t>(stages)) { s = 0; phase ^= 1u; }
         }
       }
       if (!ok) atomicOr(args.status, kStatusProducerTimeout);
@@ -162,28 +216,45 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                  (static_cast<uint32_t>(NT >> 3) << 17) |
                                  (static_cast<uint32_t>((2 * kTileCh) >> 4) << 24);
       constexpr uint32_t a_layout = KB == 2 ? 2u : 4u, a_sbo = KB == 2 ? 1024u : 512u;
-      uint32_t consumed = 0, acc_it = 0;
+      uint32_t s = 0, phase = 0, acc_it = 0;     // pipeline stage and the parity of its current use
       bool ok = true, ready = false;
       int release_stage = -1;        // stage whose MMAs are issued but whose barrier is not yet committed
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
+      if constexpr (RES) {
+        // once per cluster: metadata of the whole K extent from its staging area into TMEM
+        if (tile_first < num_tiles) {
+          if (!ptx::mbar_wait(&bar_meta[1], 0)) ok = false;
+          ptx::tc_fence_after();
+          const uint32_t e_addr = ptx::smem_u32(smem + off_e);
+          const uint32_t e_tmem = tmem_base + T::kMetaCol;
+          for (int kb = 0; kb < args.num_kb && ok; kb += 2) {
+            if (kb + 1 < args.num_kb && args.wide_cp)
+              ptx::tc_cp_128x256b_pair(e_tmem + 4 * kb, smem_desc(e_addr + kb * T::kEBlock, T::kEBlock, 128, 0));
+            else
+              for (int h = kb; h < kb + 2 && h < args.num_kb; ++h)
+                ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
+          }
+          ptx::tc_commit_pair(&bar_meta[0], 3);       // both producers: the staging area is free
+        }
+      }
+      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it) {
         const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
         if (!ptx::mbar_wait(&bar_acc_empty[buf], (acc_use & 1u) ^ 1u)) { ok = false; break; }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * NT;
-        for (int st = 0; st < num_st; ++st, ++consumed) {
-          const uint32_t s = consumed % T::kStages, use = consumed / T::kStages;
+        for (int st = 0; st < num_st; ++st) {
           const int kb0 = st * KB;
           const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
           // with a metadata warp the stage is ready when its metadata copy has completed (which
           // implies that the operands have landed); without one this thread copies it itself
           uint64_t* bar_ready = meta_warp ? bar_meta : bar_full;
-          if (!ready && !ptx::mbar_wait(&bar_ready[s], use & 1u)) { ok = false; break; }
+          if (!ready && !ptx::mbar_wait(&bar_ready[s], phase)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint32_t a_addr = ptx::smem_u32(smem + T::kOffA + s * T::kABytes);
-          const uint32_t b_addr = ptx::smem_u32(smem + T::kOffB + s * T::kBBytes);
-          const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
-          if (!meta_warp) {
-            const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
+          // resident form: weights and metadata are indexed by the K position, not by the stage
+          const uint32_t a_addr = ptx::smem_u32(smem + off_a + (RES ? st : static_cast<int>(s)) * T::kABytes);
+          const uint32_t b_addr = ptx::smem_u32(smem + off_b + s * T::kBBytes);
+          const uint32_t e_tmem = tmem_base + T::kMetaCol + (RES ? st : static_cast<int>(s)) * T::kMetaColsPerStage;
+          if (!RES && !meta_warp) {
+            const uint32_t e_addr = ptx::smem_u32(smem + off_e + s * T::kEBytes);
             if (KB == 2 && nkb == 2 && args.wide_cp) {
               // both metadata blocks of the stage in one instruction: block h is the h-th 16-byte
               // column of a 128 x 32-byte matrix whose columns lie kEBlock bytes apart
@@ -193,10 +264,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                 ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
             }
           }
-          {
-            const uint32_t s2 = (consumed + 1) % T::kStages, use2 = (consumed + 1) / T::kStages;
-            ready = mbar_peek(&bar_ready[s2], use2 & 1u);
-          }
+          const uint32_t s_next = s + 1 == static_cast<uint32_t>(stages) ? 0u : s + 1;
+          const uint32_t phase_next = s_next == 0u ? phase ^ 1u : phase;
           for (int j = 0; j < 2 * nkb; ++j) {
             const uint64_t adesc = smem_desc(a_addr + j * 32, 16, a_sbo, a_layout);
             const uint64_t bdesc = smem_desc(b_addr + (j >> 1) * T::kBBlock + (j & 1) * 64, 16, 1024, 2);
@@ -208,6 +277,11 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             }
           }
           release_stage = static_cast<int>(s);
+          // a look at the next stage's barrier once this stage's work is queued: it has usually
+          // completed by now, and a successful look is far cheaper than a wait
+          ready = mbar_peek(&bar_ready[s_next], phase_next);
+          s = s_next;
+          phase = phase_next;
         }
         if (release_stage >= 0) {
           ptx::tc_commit_pair(&bar_empty[release_stage], 3);
@@ -220,18 +294,17 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 2 + kPairEpiWarps) {
     // ------------------------------------------------------------------ metadata copier (rank 0 only)
     if (meta_warp && lane == 0 && rank == 0) {
-      uint32_t copied = 0;
+      uint32_t s = 0, phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        for (int st = 0; st < num_st; ++st, ++copied) {
-          const uint32_t s = copied % T::kStages, use = copied / T::kStages;
+      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step) {
+        for (int st = 0; st < num_st; ++st) {
           const int kb0 = st * KB;
           const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
           // the stage's previous metadata is no longer read once its MMAs have completed, which
           // the producer has already waited for before refilling the stage
-          if (!ptx::mbar_wait(&bar_full[s], use & 1u)) { ok = false; break; }
+          if (!ptx::mbar_wait(&bar_full[s], phase)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint32_t e_addr = ptx::smem_u32(smem + T::kOffE + s * T::kEBytes);
+          const uint32_t e_addr = ptx::smem_u32(smem + off_e + s * T::kEBytes);
           const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
           if (KB == 2 && nkb == 2 && args.wide_cp) {
             // both metadata blocks of the stage in one instruction: block h is the h-th 16-byte
@@ -242,6 +315,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
           }
           ptx::tc_commit_pair(&bar_meta[s], 1);      // arrives (rank 0 only) when the copy has completed
+          if (++s == static_cast<uint32_t>(stages)) { s = 0; phase ^= 1u; }
         }
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
@@ -256,7 +330,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // BF16 conversion and 32 of them stored with one stmatrix.x4.
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
-    float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
+    float* sa_s = reinterpret_cast<float*>(smem + off_sa) + (warp - 2) * NT;
     const int lane_ch = lane >> 2, tpair = (lane & 3) * 2;
     uint32_t acc_it = 0, store_it = 0;
     bool ok = true;
@@ -278,8 +352,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     };
     ptx::grid_dep_wait();             // sa is written by the kernel launched just before this one
-    if (pair < num_tiles) prefetch(pair);
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
+    if (tile_first < num_tiles) prefetch(tile_first);
+    for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
       const int ch_w = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32;
       const int tok0 = (tile / tiles_ch2) * NT;
@@ -291,7 +365,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
       for (int i = 0; i < 4; ++i) { sw[i] = sw_next[i]; bias[i] = bias_next[i]; }
       __syncwarp();
-      if (tile + num_pairs < num_tiles) prefetch(tile + num_pairs);
+      if (tile + tile_step < num_tiles) prefetch(tile + tile_step);
       int chunks = (args.m - tok0 + 31) / 32;
       chunks = chunks < NT / 32 ? chunks : NT / 32;
       if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u)) { ok = false; break; }
@@ -307,9 +381,9 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         ptx::tc_ld_16x256b_x4(t_addr + (16u << 16) + c * 32, f + 16);    // channels 16..31
       };
       auto emit = [&](const uint32_t (&f)[32], int c) {
-        uint8_t* stage = smem + T::kOffStore + ((warp - 2) * T::kStoreBufs + (store_it % T::kStoreBufs)) * T::kStoreTile;
+        uint8_t* stage = smem + off_store + ((warp - 2) * kStoreBufs + (store_it % kStoreBufs)) * T::kStoreTile;
         if (lane == 0) {
-          if constexpr (T::kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
+          if constexpr (kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
         }
         __syncwarp();
         const float2* sa_c = reinterpret_cast<const float2*>(sa_s + c * 32 + tpair);
@@ -398,7 +472,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // (unaligned output, addend, INT32 dump): lane = channel, 32 token columns per tcgen05.ld
     const int quad = warp & 3;                    // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;             // which of the quadrant's warps: chunks half, half+kPairSub, ...
-    float* sa_s = reinterpret_cast<float*>(smem + T::kOffSa) + (warp - 2) * NT;
+    float* sa_s = reinterpret_cast<float*>(smem + off_sa) + (warp - 2) * NT;
     uint32_t acc_it = 0;
     bool ok = true;
     // Scales of a tile are fetched one tile ahead into registers (the loads fly while the
@@ -422,9 +496,9 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     };
     ptx::grid_dep_wait();
     if constexpr (!INT32_OUT) {
-      if (pair < num_tiles) prefetch(pair);
+      if (tile_first < num_tiles) prefetch(tile_first);
     }
-    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++acc_it) {
+    for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
       const int ch = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
       const int tok0 = (tile / tiles_ch2) * NT;
@@ -438,7 +512,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         sw = sw_next;
         bias = bias_next;
         __syncwarp();
-        if (tile + num_pairs < num_tiles) prefetch(tile + num_pairs);
+        if (tile + tile_step < num_tiles) prefetch(tile + tile_step);
       }
       int chunks = (args.m - tok0 + 31) / 32;
       chunks = chunks < NT / 32 ? chunks : NT / 32;

@@ -83,6 +83,19 @@ def test_every_kernel_variant_is_exact(backend, oracle, oracle_c, monkeypatch, p
     assert backend.device_status() == 0
 
 
+@pytest.mark.parametrize("mode,m,k,n", [(6, 1800, 256, 9216), (8, 3700, 384, 4500), (4, 4096, 1152, 4608), (4, 7300, 1280, 2304)])
+@pytest.mark.parametrize("resident", ["0", "1"])
+def test_weights_resident_form_is_exact(backend, oracle, oracle_c, monkeypatch, mode, m, k, n, resident):
+    """Shapes on which the weights-resident form of the pair kernel applies (short K, at least two
+    token tiles per cluster), with it switched off and on: same bits either way, ragged M and N."""
+    monkeypatch.setenv("SS_RESIDENT", resident)
+    case = prepare_case(oracle, m, k, n, mode, seed=m + n)
+    out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
+                     dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), m, n)
+    assert np.array_equal(bits(out), oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"]))
+    assert backend.device_status() == 0
+
+
 @pytest.mark.parametrize("mode,m,k,n", SHAPES)
 @pytest.mark.parametrize("with_bias", [True, False])
 def test_gemm_bf16_output(backend, oracle, oracle_c, mode, m, k, n, with_bias):
