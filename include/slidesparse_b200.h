@@ -157,6 +157,23 @@ int ss_projection_fused(const void* x_bf16, int64_t x_row_stride, int64_t m, int
                         int8_t* q_scratch, float* sa_scratch,
                         void* out_bf16, int64_t out_row_stride, void* stream);
 
+/* Tensor-parallel form of ss_projection.  No counterpart in the reference (which is single-GPU).
+ * This rank computes its column shard y[m, n] (n = the shard's channels) and the GEMM epilogue
+ * stores every tile to `count` destinations instead of one: destinations[g] is the address, in
+ * this process's address space, of element [0, first column of this shard] of rank g's copy of
+ * the gathered [m, N] output (this rank's own copy included; peer copies mapped through CUDA IPC
+ * or symmetric memory), all with the row pitch out_row_stride (elements, a multiple of 8) and
+ * 16-byte aligned.  The all-gather of the N-split variant thus happens inside the kernel, tile by
+ * tile, as plain TMA stores over NVLink (no multicast); the caller orders the launch between two
+ * cross-GPU barriers (nobody still reads the buffers before; every shard has landed after). */
+int ss_projection_peers(const void* x_bf16, int64_t x_row_stride, int64_t m, int64_t k, int group,
+                        const int8_t* packed, const int32_t* meta_b200,
+                        const float* sw, const float* bias,
+                        int64_t n, int64_t pn,
+                        int8_t* q_scratch, float* sa_scratch,
+                        const void* const* destinations, int count, int64_t out_row_stride,
+                        void* stream);
+
 /* Diagnostic.  No counterpart in the reference.  Runs one CTA that issues `iterations` x 2
  * back-to-back tcgen05.mma instructions of 128 channels x token_tile tokens (sparse kind::i8 with
  * K = 64 lifted columns, or dense kind::i8 with K = 32) on operands that rotate through shared

@@ -103,6 +103,7 @@ def _declare(lib):
         "ss_quantize_lift_fused": [vp, i64, i64, i64, i32, i32, vp, vp, i64, i64, c.c_float, vp, vp, vp],
         "ss_projection_fused": [vp, i64, i64, i64, i32, i32, vp, vp, i64, i64, c.c_float,
                                 vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, vp, vp, vp, i64, vp],
+        "ss_projection_peers": [vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, i64, vp, vp, vp, i32, i64, vp],
         "ss_projection_static": [vp, i64, i64, i64, i32, vp, vp, vp, vp, i64, i64, vp, i64, vp],
         "ss_plan_create": [vp, vp, vp, vp, i64, i64, i64, i64, i32, vp],
         "ss_plan_run": [i64, vp, i64, vp, vp, vp, i64, vp],
@@ -319,6 +320,28 @@ def _projection(input, packed, metadata, scales, bias, group, n, config, output_
                                       addend.stride(0) if addend is not None else 0, n, pn,
                                       _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
     return out
+
+
+def projection_peers(input, packed, metadata, scales, bias, group, n, destinations, out_stride):
+    """Projection of this rank's column shard stored straight into every rank's gathered output.
+
+    destinations: device addresses (ints), one per rank, of element [0, first column of this shard]
+    of that rank's [m, N] BF16 buffer as mapped into this process; out_stride: its row pitch."""
+    if not input.is_cuda or input.dtype != torch.bfloat16 or input.ndim != 2:
+        raise ValueError("BF16 CUDA [m, k] input required")
+    group = group_size(int(group))
+    flat = _flatten_input(input, input.shape[-1])
+    m, k = flat.shape
+    _, pk = lifted_k(k, group)
+    pm = -(-m // 32) * 32
+    _check_weights(input.device, packed, metadata, scales, bias, pk)
+    q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
+    sa = torch.empty(pm, dtype=torch.float32, device=input.device)
+    pointers = (ctypes.c_void_p * len(destinations))(*[int(p) for p in destinations])
+    with torch.cuda.device(input.device):
+        check(library().ss_projection_peers(_ptr(flat), flat.stride(0), m, k, group, _ptr(packed), _ptr(metadata),
+                                            _ptr(scales), _ptr(bias), n, packed.shape[0], _ptr(q), _ptr(sa),
+                                            pointers, len(destinations), int(out_stride), _stream(input.device)))
 
 
 def micro_mma_rate(token_tile, sparse=True, with_metadata_copy=False, iterations=512):

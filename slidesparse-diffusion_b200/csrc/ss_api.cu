@@ -176,6 +176,26 @@ extern "C" int ss_projection_fused(const void* x, int64_t sx, int64_t m, int64_t
   return launch_gemm(a, s);
 }
 
+extern "C" int ss_projection_peers(const void* x, int64_t sx, int64_t m, int64_t k, int group,
+                                   const int8_t* packed, const int32_t* meta, const float* sw,
+                                   const float* bias, int64_t n, int64_t pn, int8_t* q_scratch,
+                                   float* sa_scratch, const void* const* destinations, int count,
+                                   int64_t out_stride, void* stream) {
+  int64_t pm, pk;
+  if (int rc = check_projection_shape(m, k, n, pn, group, &pm, &pk)) return rc;
+  SS_REQUIRE(q_scratch && sa_scratch, SS_E_ARG, "projection: scratch buffers required");
+  SS_REQUIRE(destinations && count >= 1 && count <= kMaxPeers, SS_E_ARG,
+             "projection: 1..%d destination pointers required", kMaxPeers);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (int rc = launch_quantize_lift(x, sx, m, k, group, q_scratch, sa_scratch, s)) return rc;
+  GemmArgs a{q_scratch, packed, meta, sa_scratch, sw, bias, nullptr, 0, nullptr, out_stride,
+             m, n, pm, pn, pk, false};
+  a.overlap_prologue = true;
+  a.peer_count = count;
+  for (int g = 0; g < count; ++g) a.peer_out[g] = destinations[g];
+  return launch_gemm(a, s);
+}
+
 extern "C" int ss_plan_create(const int8_t* packed, const int32_t* meta, const float* sw,
                               const float* bias, int64_t k, int64_t m, int64_t n, int64_t pn,
                               int group, int64_t* handle) {

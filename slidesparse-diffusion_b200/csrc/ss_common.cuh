@@ -67,7 +67,13 @@ struct GemmArgs {
   const void* gate = nullptr;
   int64_t gate_stride = 0;
   int64_t rows_per_batch = 0;
+  // tensor-parallel form (an extension): the BF16 result is stored to peer_count destinations
+  // (this GPU's and its peers' copies of the gathered output, each pointer already at this rank's
+  // first column) instead of `out`; all share out_stride
+  const void* peer_out[8] = {};
+  int peer_count = 0;
 };
+constexpr int kMaxPeers = 8;
 struct GemmResources {
   int threads, smem, regs, local, ctas_per_sm, token_tile, stages, tmem_cols;
 };

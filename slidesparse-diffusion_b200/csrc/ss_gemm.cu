@@ -32,6 +32,7 @@
 #include <string>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 namespace ss {
 namespace {
@@ -83,6 +84,7 @@ struct KernelArgs {
   long long gate_stride;
   int rows_per_batch;
   int res_stages;       // weights-resident form: activation pipeline stages
+  int peer_count;       // tensor-parallel form: number of destination tensor maps
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes,
@@ -350,7 +352,7 @@ int encode(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* bas
   return SS_OK;
 }
 
-struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][5][2] = {}; };
+struct DeviceInfo { int sms = 0; bool configured[5][2][2] = {}; bool pair_configured[4][6][2] = {}; };
 DeviceInfo* device_info() {
   static std::mutex mu;
   static std::unordered_map<int, DeviceInfo> table;
@@ -466,6 +468,7 @@ int launch_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t str
   k.meta_warp = 0;
   k.gate = nullptr; k.gate_stride = 0; k.rows_per_batch = 0;
   k.res_stages = 0;
+  k.peer_count = 0;
   SS_REQUIRE(k.status, SS_E_CUDA, "device status word unavailable");
   const int64_t tiles = static_cast<int64_t>(k.tiles_ch) * k.tiles_tok;
   const unsigned grid = static_cast<unsigned>(tiles < dev->sms ? tiles : dev->sms);
@@ -492,7 +495,8 @@ bool pdl_enabled() {
 template <int NT, int KB, int MODE, bool RES = false>
 int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_t stream, int res_stages = 0) {
   using T = PairTile<NT, KB>;
-  auto kernel = sparse_gemm_pair_kernel<NT, KB, MODE, RES>;
+  using Peers = std::conditional_t<MODE == kOutBf16TmaPeers, PeerMaps, NoPeers>;
+  auto kernel = sparse_gemm_pair_kernel<NT, KB, MODE, RES, Peers>;
   if (!dev->pair_configured[cfg_index][MODE][RES]) {
     SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  RES ? 227 * 1024 : T::kSmemBytes));
@@ -563,6 +567,21 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   } else {
     map_out = map_a;       // unused by the direct-store epilogues
   }
+  Peers peers{};
+  if constexpr (MODE == kOutBf16TmaPeers) {
+    SS_REQUIRE(a.peer_count >= 1 && a.peer_count <= kMaxPeers, SS_E_ARG, "gemm: 1..%d destinations", kMaxPeers);
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(a.out_stride) * 2};
+    const cuuint32_t box[2] = {32, 32};
+    for (int g = 0; g < a.peer_count; ++g) {
+      SS_REQUIRE(a.peer_out[g] && (reinterpret_cast<uintptr_t>(a.peer_out[g]) & 15) == 0, SS_E_ARG,
+                 "gemm: destination %d must be a 16-byte aligned pointer", g);
+      int rc = encode(&peers.m[g], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.peer_out[g]), dims, strides,
+                      box, CU_TENSOR_MAP_SWIZZLE_64B);
+      if (rc) return rc;
+    }
+    k.peer_count = a.peer_count;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kPairThreads);
@@ -573,7 +592,7 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream_
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = a.overlap_prologue && pdl_enabled() ? 1 : 0;
-  SS_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_e, map_out, k));
+  SS_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_e, map_out, k, peers));
   SS_CUDA(cudaGetLastError());
   return SS_OK;
 }
@@ -615,6 +634,10 @@ int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int cfg_index, cudaStream
     SS_REQUIRE(tma_ok, SS_E_ARG, "gated accumulation needs a 16-byte aligned output and row pitch");
     return launch_pair_t<NT, KB, kOutBf16GateAdd>(a, dev, cfg_index, stream);
   }
+  if (a.peer_count > 0) {
+    SS_REQUIRE(a.out_stride % 8 == 0, SS_E_ARG, "tensor-parallel stores need a row pitch that is a multiple of 8");
+    return launch_pair_t<NT, KB, kOutBf16TmaPeers>(a, dev, cfg_index, stream);
+  }
   const char* env = std::getenv("SS_STORE");          // 0 direct stores, 1 TMA stores (default)
   const int store = env ? std::atoi(env) : 1;
   if (tma_ok && store == 1) return launch_pair_t<NT, KB, kOutBf16Tma>(a, dev, cfg_index, stream);
@@ -629,7 +652,9 @@ int stage_blocks(int nt) {
 }
 
 int check_args(const GemmArgs& a) {
-  SS_REQUIRE(a.q && a.packed && a.meta && a.out, SS_E_ARG, "gemm: null pointer");
+  SS_REQUIRE(a.q && a.packed && a.meta && (a.out || a.peer_count > 0), SS_E_ARG, "gemm: null pointer");
+  SS_REQUIRE(a.peer_count == 0 || (!a.int32_out && !a.addend && !a.gate), SS_E_ARG,
+             "gemm: the tensor-parallel form excludes addend, gate and the INT32 dump");
   SS_REQUIRE(a.int32_out || (a.sa && a.sw), SS_E_ARG, "gemm: scales required");
   SS_REQUIRE(a.pk > 0 && a.pk % 128 == 0 && a.pm > 0 && a.pm % 32 == 0 && a.pn > 0 && a.pn % 32 == 0,
              SS_E_ARG, "gemm: padding mismatch (pm=%lld pn=%lld pk=%lld)", (long long)a.pm, (long long)a.pn, (long long)a.pk);
@@ -667,7 +692,7 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
     // SS_RESIDENT=0 switches the weights-resident form off
     const char* res_env = std::getenv("SS_RESIDENT");
     const bool token_tile_forced = std::getenv("SS_TOKEN_TILE") != nullptr;
-    if (!(res_env && std::atoi(res_env) == 0) && !a.int32_out && !a.addend && !token_tile_forced) {
+    if (!(res_env && std::atoi(res_env) == 0) && !a.int32_out && !a.addend && a.peer_count == 0 && !token_tile_forced) {
       // prefer the token tile that needs fewer rounds of the clusters that share a channel tile
       const int s224 = resident_stages<224>(a, dev->sms), s192 = resident_stages<192>(a, dev->sms);
       const int64_t tiles_ch2 = (a.pn + 2 * kTileCh - 1) / (2 * kTileCh), group = (dev->sms / 2) / (tiles_ch2 ? tiles_ch2 : 1);
@@ -682,7 +707,8 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
       default:  return launch_pair_nt<256, 2>(a, dev, 3, stream);
     }
   }
-  SS_REQUIRE(!a.gate, SS_E_ARG, "gemm: gated accumulation is implemented by the CTA-pair kernel only");
+  SS_REQUIRE(!a.gate && a.peer_count == 0, SS_E_ARG,
+             "gemm: gated accumulation and the tensor-parallel form are implemented by the CTA-pair kernel only");
   const int nt = pick_token_tile(a.m, a.pn, a.pk, dev->sms);
   switch (nt) {
     case 256: return stage_blocks(nt) == 2 ? launch_nt<256, 2>(a, dev, 4, stream) : launch_nt<256, 1>(a, dev, 0, stream);

@@ -74,7 +74,12 @@ enum : int {
   kOutBf16Addend = 2,  // BF16 with an addend, direct stores
   kOutBf16Tma = 3,     // BF16 staged in shared memory and written with TMA tiled stores
   kOutBf16GateAdd = 4, // as kOutBf16Tma, but out += bf16(gate[batch, channel] * y) by TMA reduction
+  kOutBf16TmaPeers = 5, // as kOutBf16Tma, but every tile is stored to several destinations (peer GPUs)
 };
+
+// Destination tensor maps of the tensor-parallel form; the other forms pass an empty struct.
+struct PeerMaps { CUtensorMap m[kMaxPeers]; };
+struct NoPeers {};
 
 // Shared-memory layout of the weights-resident form (RES): the whole K extent of the CTA's 128
 // weight rows stays in shared memory (one slab per pipeline stage of K), the metadata of the whole
@@ -93,12 +98,13 @@ struct PairResident {
   static int smem_bytes(int slabs, int stages) { return slabs * T::kABytes + stages * T::kBBytes + kFixed; }
 };
 
-template <int NT, int KB, int MODE, bool RES = false>
+template <int NT, int KB, int MODE, bool RES = false, class Peers = NoPeers>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_e,
-                        const __grid_constant__ CUtensorMap map_out, const KernelArgs args) {
+                        const __grid_constant__ CUtensorMap map_out, const KernelArgs args,
+                        const __grid_constant__ Peers peers) {
   using T = PairTile<NT, KB>;
   constexpr bool INT32_OUT = MODE == kOutInt32, HAS_ADDEND = MODE == kOutBf16Addend;
   extern __shared__ uint8_t smem_raw[];
@@ -152,6 +158,9 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     ptx::prefetch_tensormap(&map_b);
     ptx::prefetch_tensormap(&map_e);
     if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) ptx::prefetch_tensormap(&map_out);
+    if constexpr (MODE == kOutBf16TmaPeers) {
+      for (int g = 0; g < args.peer_count; ++g) ptx::prefetch_tensormap(&peers.m[g]);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(tmem_slot, kTmemCols);
@@ -320,7 +329,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
     }
-  } else if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) {
+  } else if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd || MODE == kOutBf16TmaPeers) {
     // ------------------------------------------------------------------ epilogue, TMA stores
     constexpr bool GATED = MODE == kOutBf16GateAdd;
     // The accumulator is channel-major in TMEM (lane = channel, column = token) and the output is
@@ -437,8 +446,14 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
           // beyond the last channel is not issued at all
           if (ch_w < args.n) {
-            if constexpr (GATED) ptx::tma_reduce_add_2d(&map_out, stage, ch_w, tok0 + c * 32);
-            else ptx::tma_store_2d(&map_out, stage, ch_w, tok0 + c * 32);
+            if constexpr (GATED) {
+              ptx::tma_reduce_add_2d(&map_out, stage, ch_w, tok0 + c * 32);
+            } else if constexpr (MODE == kOutBf16TmaPeers) {
+              // the same staged tile goes to this GPU's and every peer's gathered output
+              for (int g = 0; g < args.peer_count; ++g) ptx::tma_store_2d(&peers.m[g], stage, ch_w, tok0 + c * 32);
+            } else {
+              ptx::tma_store_2d(&map_out, stage, ch_w, tok0 + c * 32);
+            }
           }
           ptx::bulk_commit();
         }

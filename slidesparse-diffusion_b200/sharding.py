@@ -84,3 +84,43 @@ class TensorParallelProjection(torch.nn.Module):
         addend = None if output_addend is None else output_addend[..., start:end]
         local = self.shard(x) if addend is None else self.shard(x, output_addend=addend)
         return all_gather_columns(local, self.bounds, self.group)
+
+
+class FusedTensorParallelProjection(torch.nn.Module):
+    """N-split tensor-parallel projection whose all-gather happens inside the GEMM epilogue.
+
+    Every rank's gathered [m, N] output lives in symmetric memory (mapped into every process of
+    the group); a rank's kernel stores each tile of its column shard into all of them with plain TMA
+    stores over NVLink while the remaining tiles are still being computed, instead of running a
+    collective afterwards.  Two cross-GPU barriers frame the launch: before it nobody may still be
+    reading the buffers of the previous call, after it every shard has landed everywhere."""
+
+    def __init__(self, shard, bounds, group=None):
+        super().__init__()
+        self.shard, self.bounds = shard, list(bounds)
+        self.group = dist.group.WORLD if group is None else group
+        self.n = self.bounds[-1][1]
+        if self.n % 8:
+            raise ValueError("the gathered width must be a multiple of 8 (16-byte row pitch)")
+        self._buffers = {}
+
+    def _buffer(self, rows, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        if rows not in self._buffers:
+            out = symm_mem.empty((rows, self.n), dtype=torch.bfloat16, device=device)
+            self._buffers[rows] = (out, symm_mem.rendezvous(out, self.group))
+        return self._buffers[rows]
+
+    def forward(self, x):
+        from . import backend
+        if x.ndim != 2:
+            raise ValueError("[m, k] input required")
+        rank = dist.get_rank(self.group)
+        start, end = self.bounds[rank]
+        out, handle = self._buffer(x.shape[0], x.device)
+        destinations = [int(p) + 2 * start for p in handle.buffer_ptrs]
+        handle.barrier()
+        backend.projection_peers(x, self.shard.packed, self.shard.metadata, self.shard.scales, self.shard.bias,
+                                 self.shard.mode, end - start, destinations, self.n)
+        handle.barrier()
+        return out
