@@ -631,6 +631,26 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         tp = {"shape_mkn": [tp_m, tp_k, tp_n], "mode": "4:6", "ms": float(t.item()),
               "what": "N-split shards + NCCL all-gather of BF16 outputs, eager launches"}
+        # the same with the gather done by the GEMM epilogue's stores into every rank's buffer
+        try:
+            fused_op = sharding.FusedTensorParallelProjection(shard.to(device), sharding.shard_columns(tp_n, world))
+            for _ in range(3):
+                fused_op(tp_x)
+            barrier()
+            begin.record()
+            for _ in range(10):
+                fused_op(tp_x)
+            end.record()
+            barrier()
+            t = torch.tensor([begin.elapsed_time(end) / 10], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            same = bool(torch.equal(fused_op(tp_x), tp_op(tp_x)))
+            tp["fused_store_ms"] = float(t.item())
+            tp["fused_store_equals_nccl"] = same
+            tp["fused_what"] = ("every tile stored by the GEMM epilogue into all ranks' symmetric output buffers "
+                                "(TMA stores over NVLink), framed by two symmetric-memory barriers")
+        except Exception as e:        # noqa: BLE001 - symmetric memory may be unavailable on a box
+            tp["fused_store_error"] = f"{type(e).__name__}: {e}"
     if rank == 0:
         line = {
             "metric": "sparse_w8a8_linear_tops", "value": value, "unit": "TOPS", "n_gpus": world,
