@@ -393,12 +393,8 @@ int pick_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   return best_nt;
 }
 
-// Token tile of the CTA-pair kernel (256 channels x NT tokens per pair).  Cost model in SM
-// cycles, fitted to CUDA-event timings on B200: a block of 128 lifted columns costs about 440
-// cycles for every double-buffered tile (the main loop is bound by the issue rate of the pair's
-// tcgen05 operations, not by N) and about 560 for NT = 256, whose accumulator cannot be double
-// buffered (its epilogue, ~3000 cycles, is exposed as well); a tile costs 1500 cycles on top and
-// never less than its epilogue (~38 cycles per token column).  Ties go to the smaller tile.
+// Token tile of the CTA-pair kernel (256 channels x NT tokens per pair): the candidate with the
+// smallest rounds x cost-per-tile; ties go to the smaller tile.
 int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   if (const char* env = std::getenv("SS_TOKEN_TILE")) {
     const int v = std::atoi(env);
@@ -407,15 +403,21 @@ int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   const int64_t tiles_ch2 = (pn + 2 * kTileCh - 1) / (2 * kTileCh);
   const double num_kb = static_cast<double>(pk / kBlockK);
   const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
+  // Cost of a round of tiles in cycles, fitted to measured kernel times (graph replay) over the
+  // benchmark shapes: per 128-column block 400 / 430 / 470 / 625 cycles for token tiles of
+  // 128 / 192 / 224 / 256 (256 has one pipeline stage less and no metadata warp), plus a per-tile
+  // part of about 12 cycles per token column (epilogue tail, barrier round trips); a tile cannot
+  // be faster than its epilogue (about 18 cycles per token column).
   const int cand[4] = {128, 192, 224, 256};
+  const double per_block[4] = {400.0, 430.0, 470.0, 625.0};
   double best = 0;
   int best_nt = 224;
   for (int i = 0; i < 4; ++i) {
     const int nt = cand[i];
     const int64_t tiles = tiles_ch2 * ((m + nt - 1) / nt);
     const int64_t rounds = (tiles + pairs - 1) / pairs;
-    const double main = num_kb * (nt == 256 ? 560.0 : 420.0) + 1500.0 + (nt == 256 ? 3000.0 : 0.0);
-    const double epilogue = 38.0 * nt;
+    const double main = num_kb * per_block[i] + 12.0 * nt;
+    const double epilogue = 18.0 * nt;
     const double cost = static_cast<double>(rounds) * (main > epilogue ? main : epilogue);
     if (best == 0 || cost < best * 0.999) { best = cost; best_nt = nt; }
   }
