@@ -403,22 +403,22 @@ int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms) {
   const int64_t tiles_ch2 = (pn + 2 * kTileCh - 1) / (2 * kTileCh);
   const double num_kb = static_cast<double>(pk / kBlockK);
   const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
-  // Cost of a round of tiles in cycles, fitted to measured kernel times (graph replay) over the
-  // benchmark shapes: per 128-column block 400 / 430 / 470 / 625 cycles for token tiles of
-  // 128 / 192 / 224 / 256 (256 has one pipeline stage less and no metadata warp), plus a per-tile
-  // part of about 12 cycles per token column (epilogue tail, barrier round trips); a tile cannot
-  // be faster than its epilogue (about 18 cycles per token column).
+  // Cost of one tile in cycles = blocks of 128 lifted columns x per-block cost + per-tile cost,
+  // both fitted per token tile to measured kernel times (graph replay) over the benchmark shapes
+  // (a long-K and a short-K shape each): 330 / 348 / 343 / 472 cycles per block and 2300 / 2650 /
+  // 3400 / 4800 per tile for token tiles of 128 / 192 / 224 / 256 (256 has one pipeline stage less
+  // and no metadata warp; the per-tile part is the epilogue tail and the barrier round trips).
+  // Over the eleven shapes of the fit the model's choice costs 0.2 % more than the best tile.
   const int cand[4] = {128, 192, 224, 256};
-  const double per_block[4] = {400.0, 430.0, 470.0, 625.0};
+  const double per_block[4] = {330.0, 348.0, 343.0, 472.0};
+  const double per_tile[4] = {2300.0, 2650.0, 3400.0, 4800.0};
   double best = 0;
   int best_nt = 224;
   for (int i = 0; i < 4; ++i) {
     const int nt = cand[i];
     const int64_t tiles = tiles_ch2 * ((m + nt - 1) / nt);
     const int64_t rounds = (tiles + pairs - 1) / pairs;
-    const double main = num_kb * per_block[i] + 12.0 * nt;
-    const double epilogue = 18.0 * nt;
-    const double cost = static_cast<double>(rounds) * (main > epilogue ? main : epilogue);
+    const double cost = static_cast<double>(rounds) * (num_kb * per_block[i] + per_tile[i]);
     if (best == 0 || cost < best * 0.999) { best = cost; best_nt = nt; }
   }
   return best_nt;
