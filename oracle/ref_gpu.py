@@ -19,6 +19,12 @@ not sm_80 (dualscale_sm80.cu:294).  All configurations share one epilogue arithm
     python oracle/ref_gpu.py build    [--reference /path/to/SlideSparse-Diffusion]     (CPU box)
     python oracle/ref_gpu.py generate --out tests/golden/ref_gpu.npz                   (GPU box)
     python oracle/ref_gpu.py time                                                      (GPU box)
+    python oracle/ref_gpu.py digest --out file.json                                    (GPU box)
+
+`digest` runs the reference's projection at the FULL sizes of the benchmark configurations on
+seeded inputs and writes SHA-256 digests of its INT8 activations, token scales and BF16 output;
+tests/test_gpu_reference.py launches it as a child process and compares them with the digests of
+this library's outputs on the same inputs.
 
 `time` prints, for a few benchmark shapes, the device time of the reference's quantize and run
 (configurations 14-16 only, see above: small tiles, not the configurations the reference's own
@@ -128,6 +134,53 @@ def generate(out):
     print(f"wrote {out}: {len(CASES)} cases on {torch.cuda.get_device_name(0)}")
 
 
+# full-size cases of the benchmark configurations: (mode, m, k, n, config)
+FULL_CASES = (
+    (4, 4096, 1152, 4608, 16),        # configs[0]
+    (6, 1536, 3072, 9216, 16),        # FLUX fused QKV
+    (8, 1536, 12288, 3072, 15),       # FLUX MLP fc2
+    (8, 4096, 3072, 12288, 16),       # FLUX MLP fc1, M swept
+    (4, 2048, 4608, 1152, 14),        # DiT FFN-out
+    (8, 8192, 1152, 3456, 16),        # PixArt-Sigma fused QKV
+    (6, 2048, 2432, 9728, 16),        # SD3.5 image FFN-in
+    (6, 666, 9728, 2432, 15),         # SD3.5 text FFN-out
+)
+
+
+def full_case_inputs(oracle, index, mode, m, k, n):
+    import torch
+    x = oracle.make_activation(m, k, seed=400 + index)
+    qweight, scales = oracle.make_weight(n, k, mode, seed=500 + index)
+    bias = (0.1 * torch.randn(n, generator=torch.Generator().manual_seed(600 + index))).float().numpy()
+    return x, qweight, scales, bias
+
+
+def digest(out):
+    import json
+    import torch
+    sys.path.insert(0, str(HERE.parent))
+    from oracle import ss_oracle as oracle
+    if "slidesparse_diffusion_b200" in sys.modules:
+        raise RuntimeError("the B200 package is loaded: both libraries define the sdacc_* operator namespaces")
+    torch.ops.load_library(str(TARGET))
+    front, gemm = torch.ops.sdacc_mild_projection_sm80, torch.ops.sdacc_dualscale_sm80
+    dev = torch.device("cuda", 0)
+    rows = []
+    for index, (mode, m, k, n, config) in enumerate(FULL_CASES):
+        x, qweight, scales, bias = full_case_inputs(oracle, index, mode, m, k, n)
+        _, pk = oracle.lifted_k(k, mode)
+        packed, meta = gemm.pack_cpu(torch.from_numpy(oracle.slide_weight(qweight, mode)), pk)
+        q, sa = front.quantize(x.to(dev), mode)
+        y = front.projection(x.to(dev), packed.to(dev), meta.to(dev), torch.from_numpy(scales).to(dev),
+                             torch.from_numpy(bias).to(dev), mode, n, config, None)
+        torch.cuda.synchronize()
+        sha = lambda t: hashlib.sha256(t.contiguous().cpu().numpy().tobytes()).hexdigest()
+        rows.append(dict(case=[mode, m, k, n, config], q=sha(q), sa=sha(sa), y=sha(y.view(torch.int16)),
+                         packed=sha(packed)))
+    Path(out).write_text(json.dumps({"device": torch.cuda.get_device_name(0), "rows": rows}))
+    print(f"wrote {out}: {len(rows)} full-size cases")
+
+
 def time_reference():
     import json
     import torch
@@ -175,7 +228,7 @@ def time_reference():
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("action", choices=("build", "generate", "time"))
+    parser.add_argument("action", choices=("build", "generate", "time", "digest"))
     parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE", "/root/reference"))
     parser.add_argument("--out", default=str(HERE.parent / "tests" / "golden" / "ref_gpu.npz"))
     parser.add_argument("--force", action="store_true")
@@ -184,5 +237,7 @@ if __name__ == "__main__":
         print(build(args.reference, args.force))
     elif args.action == "time":
         time_reference()
+    elif args.action == "digest":
+        digest(args.out)
     else:
         generate(args.out)
