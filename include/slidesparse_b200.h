@@ -82,6 +82,35 @@ int ss_weight_grid_device(const float* w, int64_t n, int64_t k, int8_t* qweight,
 int ss_pack_device(const int8_t* qweight, int64_t n, int64_t k, int group,
                    int8_t* packed, int32_t* meta_b200, int32_t* status, void* stream);
 
+/* ---- weight preparation: fixed-order shared-curvature pruning with joint INT8 rounding ------ */
+
+/* One column block [start, start+width) of compress (diffusion_research/reconstruction.py:86-112):
+ * w fp32 [rows,columns] on the device, updated in place to the finalised values of the block;
+ * upper fp32 [columns,columns] is the shared factor (factor_hessian, :18-39); scales [rows];
+ * zeros uint8 [rows,columns] receives the selected zeros of the block, errors [rows,width] the
+ * per-column errors, losses [rows] accumulates the proxy loss.  joint != 0 rounds each column to
+ * the INT8 grid as it is finalised ("joint"), 0 leaves it ("prune_then_rtn").  start must be a
+ * multiple of group and width at most ss_obs_max_blocksize(). */
+int ss_obs_block(float* w, int64_t rows, int64_t columns, int64_t start, int64_t width,
+                 const float* upper, const float* scales, int group, int joint,
+                 uint8_t* zeros, float* errors, float* losses, void* stream);
+
+/* w[:, start+width:] -= errors @ upper[start:start+width, start+width:], each sum taken as
+ * fma(e, u, acc) in increasing k.  diffusion_research/reconstruction.py:113-114. */
+int ss_obs_trailing(float* w, int64_t rows, int64_t columns, int64_t start, int64_t width,
+                    const float* upper, const float* errors, void* stream);
+
+/* Export of compress (diffusion_research/reconstruction.py:117-127): qweight = clamp(rint(w/scale))
+ * with the selected zeros forced to 0.  status (device int32[1], zeroed by the caller) gets bit 0
+ * if check_grid and some qweight*scale differs from w, bit 1 if a complete group of `group`
+ * columns holds more than group-2 nonzeros. */
+int ss_obs_finish(const float* w, const float* scales, const uint8_t* zeros, int64_t rows,
+                  int64_t columns, int group, int check_grid, int8_t* qweight, int32_t* status,
+                  void* stream);
+
+/* Widest column block ss_obs_block accepts (shared-memory bound).  No counterpart in the reference. */
+int ss_obs_max_blocksize(void);
+
 /* ---- front-end: dynamic per-token quantisation + slide expansion ------------------------ */
 
 /* x: BF16 [m,k], unit column stride, row stride x_row_stride elements.  Writes q [pm,pk] and

@@ -13,6 +13,7 @@
  */
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 static float bf16_to_f32(uint16_t b) {
@@ -175,4 +176,76 @@ void sso_epilogue_gated(const int32_t* acc, const float* sa, const float* sw, co
       const float z = bf16_to_f32(f32_to_bf16(bf16_to_f32(gate[(i / rows_per_batch) * gate_stride + j]) * y));
       out[i * n + j] = f32_to_bf16(bf16_to_f32(residual[i * n + j]) + z);
     }
+}
+
+/* Fixed-order, shared-curvature pruning with joint INT8 rounding
+ * (diffusion_research/reconstruction.py:55-133, compress).  w [rows,columns] is updated in place
+ * to the compensated weight (dead columns must already be zero), zeros receives the selected
+ * zeros, losses the proxy loss per row; upper is the shared factor [columns,columns].  Inside a
+ * column block every operation is the separately rounded fp32 operation of the reference's
+ * tensor expressions (:95-110; its k=1 matrix product rounds each product once); the block's
+ * errors are applied to the later columns (:113-114) as acc = fma(e, u, acc) from 0 in
+ * increasing k followed by one subtraction — the reference leaves the summation order of that
+ * product to its BLAS, so results agree with it to rounding there.  Ties between equal scores go
+ * to the lower column (torch.topk does not define them). */
+static float sso_round_to_grid(float v, float s) {
+  float r = rintf(v / s);
+  return r < -128.f ? -128.f : (r > 127.f ? 127.f : r);
+}
+
+void sso_obs_compress(float* w, int64_t rows, int64_t columns, const float* upper, const float* scales,
+                      int group, int blocksize, int joint, uint8_t* zeros, float* losses) {
+  memset(zeros, 0, (size_t)(rows * columns));
+  for (int64_t r = 0; r < rows; ++r) losses[r] = 0.f;
+  for (int64_t start = 0; start < columns; start += blocksize) {
+    const int64_t stop = start + blocksize < columns ? start + blocksize : columns;
+    const int64_t width = stop - start;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+      float* local = (float*)malloc(sizeof(float) * (size_t)width * 3);
+      float* done = local + width;
+      float* err = done + width;
+      float* wr = w + r * columns;
+      uint8_t* zr = zeros + r * columns;
+      for (int64_t j = 0; j < width; ++j) local[j] = wr[start + j];
+      for (int64_t index = 0; index < width; ++index) {
+        if (index % group == 0) {
+          const int64_t span = group < width - index ? group : width - index;
+          const int64_t remove = 2 - (group - span) > 0 ? 2 - (group - span) : 0;
+          int64_t first = -1, second = -1;
+          float best = 0.f;
+          for (int64_t g = 0; g < span; ++g) {
+            const float v = local[index + g], d = upper[(start + index + g) * columns + start + index + g];
+            const float score = (v * v) / (d * d);
+            if (first < 0 || score < best) { first = g; best = score; }
+          }
+          if (remove > 1)
+            for (int64_t g = 0; g < span; ++g) {
+              if (g == first) continue;
+              const float v = local[index + g], d = upper[(start + index + g) * columns + start + index + g];
+              const float score = (v * v) / (d * d);
+              if (second < 0 || score < best) { second = g; best = score; }
+            }
+          if (remove > 0) zr[start + index + first] = 1;
+          if (remove > 1) zr[start + index + second] = 1;
+        }
+        const float current = local[index];
+        float fin = joint ? sso_round_to_grid(current, scales[r]) * scales[r] : current;
+        if (zr[start + index]) fin = 0.f;
+        const float* frow = upper + (start + index) * columns + start;
+        const float e = (current - fin) / frow[index];
+        losses[r] = losses[r] + (e * e) * 0.5f;
+        done[index] = fin;
+        err[index] = e;
+        for (int64_t j = index; j < width; ++j) local[j] = local[j] - e * frow[j];
+      }
+      for (int64_t j = 0; j < width; ++j) wr[start + j] = done[j];
+      for (int64_t c = stop; c < columns; ++c) {
+        float acc = 0.f;
+        for (int64_t k = 0; k < width; ++k) acc = fmaf(err[k], upper[(start + k) * columns + c], acc);
+        wr[c] = wr[c] - acc;
+      }
+      free(local);
+    }
+  }
 }

@@ -127,3 +127,23 @@ def epilogue_gated(acc, sa, sw, bias, gate_bits, rows_per_batch, residual_bits):
     load().sso_epilogue_gated(_p(acc), _p(sa), _p(sw), _p(b) if b is not None else None, _p(gate), _i64(gate.shape[1]),
                               _i64(rows_per_batch), _p(residual), _i64(m), _i64(n), _p(out))
     return out
+
+
+def obs_compress(weight, upper, dead, scales, group, blocksize=192, joint=True):
+    """compress (diffusion_research/reconstruction.py:55-133) on fp32 numpy arrays.  Returns
+    qweight int8, zeros bool, compensated fp32, proxy_loss fp32."""
+    w = np.array(weight, dtype=np.float32, order="C", copy=True)
+    dead = np.asarray(dead, dtype=bool)
+    w[:, dead] = 0
+    rows, columns = w.shape
+    u = np.ascontiguousarray(upper, dtype=np.float32)
+    s = np.ascontiguousarray(scales, dtype=np.float32)
+    zeros = np.zeros((rows, columns), dtype=np.uint8)
+    losses = np.zeros(rows, dtype=np.float32)
+    load().sso_obs_compress(_p(w), _i64(rows), _i64(columns), _p(u), _p(s), ctypes.c_int(group),
+                            ctypes.c_int(blocksize), ctypes.c_int(1 if joint else 0), _p(zeros), _p(losses))
+    zeros = zeros.astype(bool)
+    zeros[:, dead] = True
+    q = np.clip(np.rint(w / s[:, None]), -128, 127).astype(np.int8)
+    q[zeros] = 0
+    return q, zeros, w, losses

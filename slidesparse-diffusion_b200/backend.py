@@ -23,7 +23,7 @@ from .packing import group_size, lifted_k
 
 SS_E_ARG, SS_E_CUDA, SS_E_FORMAT, SS_E_HANDLE, SS_E_DEVICE, SS_E_LIMIT = -1, -2, -3, -4, -5, -6
 LIBRARY_NAME = "libslidesparse_b200.so"
-SOURCES = ("ss_api.cu", "ss_gemm.cu", "ss_frontend.cu", "ss_pack.cu", "ss_noalloc.cu", "ss_micro.cu")
+SOURCES = ("ss_api.cu", "ss_gemm.cu", "ss_frontend.cu", "ss_pack.cu", "ss_noalloc.cu", "ss_micro.cu", "ss_obs.cu")
 ARCH = "sm_100a"
 VALID_CONFIGS = (0, 1, 2, 3, 4, 5, 6, 11, 12, 13, 14, 15, 16, 17)
 
@@ -96,6 +96,9 @@ def _declare(lib):
         "ss_meta_convert": [vp, vp, i64, i64, i32],
         "ss_weight_grid_device": [vp, i64, i64, vp, vp, vp],
         "ss_pack_device": [vp, i64, i64, i32, vp, vp, vp, vp],
+        "ss_obs_block": [vp, i64, i64, i64, i64, vp, vp, i32, i32, vp, vp, vp, vp],
+        "ss_obs_trailing": [vp, i64, i64, i64, i64, vp, vp, vp],
+        "ss_obs_finish": [vp, vp, vp, i64, i64, i32, i32, vp, vp, vp],
         "ss_quantize_lift": [vp, i64, i64, i64, i32, vp, vp, vp],
         "ss_gemm_run": [vp, vp, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, i64, vp],
         "ss_gemm_int32": [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp],
@@ -116,6 +119,7 @@ def _declare(lib):
     for name, args in sigs.items():
         fn = getattr(lib, name)
         fn.argtypes, fn.restype = args, i32
+    lib.ss_obs_max_blocksize.argtypes, lib.ss_obs_max_blocksize.restype = [], i32
     return lib
 
 

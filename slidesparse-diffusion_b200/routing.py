@@ -95,12 +95,15 @@ class OrdinaryProxy(torch.nn.Module):
         return self.state.output(x, prologue, gated_residual)
 
 
-def pack_members(members, mode, protected_prefix=0):
+def pack_members(members, mode, protected_prefix=0, curvature=None):
     """PackedLinear for the concatenation of dense members on their device, prepared entirely on
-    the GPU: magnitude pruning to the (L-2):L pattern (a synthetic stand-in for the reference's
-    OBS pruner: the 2 smallest-|w| lanes of every aligned group of L go, ties to the lowest index;
-    lanes missing from a tail group count as already pruned), the per-channel INT8
-    grid (`ss_weight_grid_device`) and slide + 2:4 packing (`ss_pack_device`)."""
+    the GPU.  With a `curvature` (reconstruction.factor_hessian of the members' shared input) the
+    weight goes through the curvature-compensated pruner with joint INT8 rounding
+    (`reconstruction.compress`); without one, through magnitude pruning to the (L-2):L pattern
+    (the 2 smallest-|w| lanes of every aligned group of L go, ties to the lowest index; lanes
+    missing from a tail group count as already pruned) and the per-channel INT8 grid
+    (`ss_weight_grid_device`).  Either way slide + 2:4 packing happens on the device
+    (`ss_pack_device`)."""
     import ctypes
     from . import backend
     from .packing import group_size, lifted_k
@@ -112,23 +115,29 @@ def pack_members(members, mode, protected_prefix=0):
         bias = torch.cat([m.bias for m in members]).detach().float().contiguous()
     n, k = weight.shape
     device = weight.device
-    pad = (-k) % length
-    groups = torch.nn.functional.pad(weight.abs(), (0, pad), value=-1.0).reshape(n, -1, length)
-    mask = torch.zeros_like(groups, dtype=torch.bool)
-    for _ in range(2):                      # argmin returns the lowest index among ties
-        first = groups.argmin(dim=-1, keepdim=True)
-        mask.scatter_(-1, first, True)
-        groups.scatter_(-1, first, float("inf"))
-    mask = mask.reshape(n, -1)[:, :k]
     lib = backend.library()
     stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-    qweight = torch.empty((n, k), dtype=torch.int8, device=device)
-    scales = torch.empty(n, dtype=torch.float32, device=device)
+    if curvature is not None:
+        from .reconstruction import compress
+        prepared = compress(weight, curvature, length, allow_tail=bool(k % length))
+        qweight, scales = prepared["qweight"], prepared["scales"]
+    else:
+        pad = (-k) % length
+        groups = torch.nn.functional.pad(weight.abs(), (0, pad), value=-1.0).reshape(n, -1, length)
+        mask = torch.zeros_like(groups, dtype=torch.bool)
+        for _ in range(2):                      # argmin returns the lowest index among ties
+            first = groups.argmin(dim=-1, keepdim=True)
+            mask.scatter_(-1, first, True)
+            groups.scatter_(-1, first, float("inf"))
+        mask = mask.reshape(n, -1)[:, :k]
+        qweight = torch.empty((n, k), dtype=torch.int8, device=device)
+        scales = torch.empty(n, dtype=torch.float32, device=device)
+        with torch.cuda.device(device):
+            weight.masked_fill_(mask, 0.0)
+            backend.check(lib.ss_weight_grid_device(ctypes.c_void_p(weight.data_ptr()), n, k,
+                                                    ctypes.c_void_p(qweight.data_ptr()),
+                                                    ctypes.c_void_p(scales.data_ptr()), stream))
     with torch.cuda.device(device):
-        weight.masked_fill_(mask, 0.0)
-        backend.check(lib.ss_weight_grid_device(ctypes.c_void_p(weight.data_ptr()), n, k,
-                                                ctypes.c_void_p(qweight.data_ptr()),
-                                                ctypes.c_void_p(scales.data_ptr()), stream))
         _, pk = lifted_k(k, length)
         pn = -(-n // 32) * 32
         packed = torch.empty((pn, pk // 2), dtype=torch.int8, device=device)

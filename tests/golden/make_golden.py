@@ -13,6 +13,9 @@ file.  Inputs are seeded numpy draws stored in the fixtures together with the ou
   lift.npz         activation_indices / lift_integer
                    (diffusion_research/integrations/cachequant/native_sparse.py:11-23)
   weight_grid.npz  channel_scales / round_signed (diffusion_research/reconstruction.py:41-53)
+  reconstruction.npz  factor_hessian and compress (diffusion_research/reconstruction.py:18-39,
+                   55-133) on CPU: single-block cases (bit-reproducible) and multi-block cases
+                   (the trailing update goes through the BLAS the reference was run with)
 """
 import argparse
 import importlib.util
@@ -31,6 +34,46 @@ def load_file(name, path):
     module = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(module)
     return module
+
+
+RECONSTRUCTION_CASES = (
+    # rows, columns, group, blocksize, method, allow_tail, dead columns, explicit scales
+    (12, 48, 4, 192, "joint", False, (), False),
+    (10, 48, 6, 192, "joint", False, (7, 30), False),
+    (9, 64, 8, 192, "prune_then_rtn", False, (), False),
+    (8, 44, 8, 192, "joint", True, (), False),
+    (7, 47, 6, 192, "joint", True, (), True),
+    (16, 96, 6, 24, "joint", False, (50,), False),
+    (8, 64, 4, 16, "joint", False, (), True),
+    (8, 79, 8, 32, "prune_then_rtn", True, (), False),
+)
+
+
+def reconstruction_fixture(ref):
+    recon = load_file("ref_reconstruction", ref / "sdacc/diffusion_research/reconstruction.py")
+    rng = np.random.default_rng(20260)
+    out = {"cases": np.array([(r, c, g, b, m == "joint", t, e) for r, c, g, b, m, t, _, e in RECONSTRUCTION_CASES],
+                             dtype=np.int64)}
+    for i, (rows, columns, group, blocksize, method, allow_tail, dead, explicit) in enumerate(RECONSTRUCTION_CASES):
+        x = rng.normal(0, 1, size=(256, columns)).astype(np.float32)
+        x[:, rng.permutation(columns)[:2]] *= 8
+        x[:, list(dead)] = 0
+        hessian = torch.from_numpy(x.T @ x / 256)
+        hessian = (hessian + hessian.T) / 2
+        weight = torch.from_numpy(rng.normal(0, 0.02, size=(rows, columns)).astype(np.float32))
+        curvature = recon.factor_hessian(hessian, damping=.01)
+        scales = torch.from_numpy(rng.uniform(2e-4, 6e-4, size=rows).astype(np.float32)) if explicit else None
+        result = recon.compress(weight, curvature, group, method=method, blocksize=blocksize, scales=scales,
+                                allow_tail=allow_tail)
+        out[f"weight{i}"] = weight.numpy()
+        out[f"hessian{i}"] = hessian.numpy()
+        out[f"upper{i}"] = curvature.upper.numpy()
+        out[f"dead{i}"] = curvature.dead.numpy()
+        out[f"damping{i}"] = np.float64(curvature.damping)
+        out[f"scales_in{i}"] = scales.numpy() if explicit else np.zeros(0, np.float32)
+        for key in ("qweight", "scales", "zeros", "compensated", "proxy_loss"):
+            out[f"{key}{i}"] = result[key].numpy()
+    np.savez_compressed(HERE / "reconstruction.npz", **out)
 
 
 def structured_weight(rng, n, k, l, density=0.9):
@@ -110,6 +153,7 @@ def main():
     scales = recon.channel_scales(w)
     q = recon.round_signed(w, scales[:, None])
     np.savez_compressed(HERE / "weight_grid.npz", w=w.numpy(), scales=scales.numpy(), q=q.numpy().astype(np.int8))
+    reconstruction_fixture(ref)
     print("wrote", [p.name for p in sorted(HERE.glob("*.npz"))])
 
 
