@@ -27,6 +27,8 @@ channel shards, no collective); value = all ranks' operations / max-over-ranks t
 (model forward on the CFG pair + guidance + sampler update, one CUDA graph) of a random-init
 transformer of that shape, with the routed projections sparse and with the same projections dense
 BF16 (dense measured before and after the sparse run); data-parallel over images when N > 1.
+`--workload compress` times the weight preparation (`reconstruction.compress`) of three weight
+shapes against the oracle port of the reference's algorithm on the host cores.
 """
 import argparse
 import json
@@ -291,6 +293,59 @@ def run_micro(local_rank):
                       "config": {"workload": "micro"}, "rows": rows}))
 
 
+def run_compress(args, local_rank):
+    """Weight preparation (curvature-compensated pruning with joint INT8 rounding) of three weight
+    shapes of the configurations: device time of `reconstruction.compress` against the oracle port
+    of the reference's algorithm on the host cores over a sample of the rows (rows are independent)."""
+    import numpy as np
+    import torch
+    from __graft_entry__ import load_package, load_oracle
+    sdk = load_package()
+    sdk.load_native()
+    from slidesparse_diffusion_b200 import reconstruction
+    _, oracle_c = load_oracle()
+    oracle_c.build()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    rows_out = []
+    sample_rows = 32
+    for name, rows, columns, group in (("pixart fc1 2:4", 4608, 1152, 4), ("flux qkv 4:6", 9216, 3072, 6),
+                                       ("flux fc2 6:8", 3072, 12288, 8)):
+        gen = torch.Generator(device=dev).manual_seed(rows + columns)
+        x = torch.randn(2 * columns, columns, device=dev, generator=gen)
+        x[:, :: 97] *= 8
+        hessian = x.T @ x / x.shape[0]
+        weight = 0.02 * torch.randn(rows, columns, device=dev, generator=gen)
+        curvature = reconstruction.factor_hessian((hessian + hessian.T) / 2)
+        times = []
+        for _ in range(max(args.warmup, 1) + max(1, min(args.steps, 5))):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            result = reconstruction.compress(weight, curvature, group)
+            end.record()
+            torch.cuda.synchronize()
+            times.append(begin.elapsed_time(end))
+        gpu_ms = statistics.median(times[max(args.warmup, 1):])
+        row = {"weight": name, "rows": rows, "columns": columns, "group": group, "gpu_ms": gpu_ms,
+               "mean_proxy_loss": float(result["proxy_loss"].mean())}
+        if not args.no_cpu:
+            upper = curvature.upper.cpu().numpy()
+            dead = curvature.dead.cpu().numpy()
+            sample = weight[:sample_rows].cpu().numpy()
+            scales = result["scales"][:sample_rows].cpu().numpy()
+            t0 = time.perf_counter()
+            q, _, _, _ = oracle_c.obs_compress(sample, upper, dead, scales, group)
+            cpu_s = time.perf_counter() - t0
+            row["cpu_sample_rows"] = sample_rows
+            row["cpu_ms_scaled_to_all_rows"] = cpu_s * 1e3 * rows / sample_rows
+            row["cpu_cores"] = os.cpu_count()
+            row["sample_equal"] = bool(np.array_equal(q, result["qweight"][:sample_rows].cpu().numpy()))
+        rows_out.append(row)
+    print(json.dumps({"metric": "compress_ms", "unit": "ms", "n_gpus": 1, "data": "synthetic", "dtype": "f32",
+                      "higher_is_better": False, "config": {"workload": "compress", "blocksize": 192,
+                                                             "method": "joint"}, "rows": rows_out}))
+
+
 def run_denoise(args, rank, world, local_rank):
     """Denoise-step latency: sparse routed projections against dense BF16 on the same model."""
     import torch
@@ -390,7 +445,8 @@ def main():
     parser.add_argument("--tokens", type=str, default=None, help="comma-separated M values (debug)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     parser.add_argument("--workload", default="flux_sweep",
-                        choices=("flux_sweep", "shapes", "micro", "dit-xl-512", "pixart-sigma-1024", "sd35-large-512"))
+                        choices=("flux_sweep", "shapes", "micro", "compress", "dit-xl-512", "pixart-sigma-1024",
+                                 "sd35-large-512"))
     parser.add_argument("--images", type=int, default=1, help="images per forward in the denoise workloads")
     parser.add_argument("--blocks", type=int, default=None, help="override the block count (debug)")
     args = parser.parse_args()
@@ -408,6 +464,10 @@ def main():
     if args.workload == "micro":
         if rank == 0:
             run_micro(local_rank)
+        return
+    if args.workload == "compress":
+        if rank == 0:
+            run_compress(args, local_rank)
         return
     if args.workload != "flux_sweep":
         run_denoise(args, rank, world, local_rank)

@@ -60,7 +60,7 @@ def _synthetic(rows, columns, seed, dead=()):
     (257, 512, 8, 192, "prune_then_rtn", ()),
     (64, 1152, 6, 96, "joint", ()),
     (33, 410, 8, 200, "joint", (409,)),          # tail group of 2 columns
-    (1000, 216, 4, 216, "joint", ()),            # widest block the kernel holds
+    (1000, 224, 4, 224, "joint", ()),            # widest usable block the kernel holds
 ])
 def test_kernels_match_the_oracle(recon, oracle_c, rows, columns, group, blocksize, method, dead):
     assert blocksize <= recon.max_blocksize()
