@@ -3,8 +3,8 @@
 // (reference: sdacc/diffusion_research/reconstruction.py:55-133, `compress`).
 //
 // Output rows are independent and all share one curvature factor, so a column block is processed
-// by one warp per row: the row's slice lives in shared memory next to the block's factor tile, the
-// warp walks the columns in order (selection at each group start, rounding, error, rank-one
+// by eight lanes per row: the row's slice lives in shared memory next to the block's factor tile,
+// the lanes walk the columns in order (selection at each group start, rounding, error, rank-one
 // update of the columns still open) and the errors of the block are then applied to all later
 // columns by an fp32 GEMM with a fixed summation order.  Every floating-point operation is a
 // separately rounded IEEE operation in the order the reference's tensor expressions apply them

@@ -4,7 +4,7 @@ to the pruned INT8 `qweight` and per-channel `scales` that `PackedLinear.prepare
 Same functions, arguments, errors and result keys as the reference's
 `sdacc/diffusion_research/reconstruction.py` (`factor_hessian` :18-39, `channel_scales` :41-49,
 `round_signed` :52-53, `compress` :55-133).  `compress` runs on the GPU through the C-ABI kernels
-(`ss_obs_block`, `ss_obs_trailing`, `ss_obs_finish`): one warp per output row walks a column block
+(`ss_obs_block`, `ss_obs_trailing`, `ss_obs_finish`): eight lanes per output row walk a column block
 in order, the block's errors reach the later columns through an fp32 GEMM with a fixed summation
 order, so a result does not depend on the GPU, the grid or the run.  There is no CPU path: a CPU
 weight is refused.
