@@ -135,3 +135,30 @@ def test_pack_members_with_a_curvature(sdk, recon, oracle, oracle_c):
     expect = oracle.projection(act, q, scales, bias, 8)["out_bits"]
     y = op(act.to(dev))
     assert np.array_equal(y.view(torch.int16).cpu().numpy().view(np.uint16), expect)
+
+
+def test_full_size_weight_sample_rows_equal_the_oracle(recon, oracle_c):
+    """FLUX fused-QKV weight (9216 x 3072, 4:6): rows are independent, so 32 rows spread over the
+    weight are checked bit for bit against the oracle and every row for the (L-2):L structure and
+    the frozen grid."""
+    rows, columns, group = 9216, 3072, 6
+    dev = "cuda:0"
+    gen = torch.Generator(device=dev).manual_seed(77)
+    x = torch.randn(2 * columns, columns, device=dev, generator=gen)
+    x[:, ::97] *= 8
+    hessian = x.T @ x / x.shape[0]
+    weight = 0.02 * torch.randn(rows, columns, device=dev, generator=gen)
+    curvature = recon.factor_hessian((hessian + hessian.T) / 2)
+    result = recon.compress(weight, curvature, group)
+    q = result["qweight"]
+    assert int((q.reshape(rows, -1, group) != 0).sum(-1).max()) <= group - 2
+    assert torch.equal(q.float() * result["scales"][:, None], result["compensated"])
+    assert int(result["zeros"].sum()) == rows * columns // group * 2
+    pick = torch.arange(0, rows, rows // 32, device=dev)[:32]
+    expect_q, expect_zeros, expect_w, expect_loss = oracle_c.obs_compress(
+        weight[pick].cpu().numpy(), curvature.upper.cpu().numpy(), curvature.dead.cpu().numpy(),
+        result["scales"][pick].cpu().numpy(), group)
+    assert np.array_equal(q[pick].cpu().numpy(), expect_q)
+    assert np.array_equal(result["zeros"][pick].cpu().numpy(), expect_zeros)
+    assert np.array_equal(_bits(result["compensated"][pick]), expect_w.view(np.uint32))
+    assert np.array_equal(_bits(result["proxy_loss"][pick]), expect_loss.view(np.uint32))
