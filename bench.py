@@ -693,8 +693,11 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         tp = {"shape_mkn": [tp_m, tp_k, tp_n], "mode": "4:6", "ms": float(t.item()),
               "what": "N-split shards + NCCL all-gather of BF16 outputs, eager launches"}
-        # the same with the gather done by the GEMM epilogue's stores into every rank's buffer
+        # the same with the gather done by the GEMM epilogue's stores into every rank's buffer; this
+        # variant has been run on 2 GPUs only, so larger worlds take it only when asked to
         try:
+            if world > 2 and os.environ.get("SS_BENCH_TP_FUSED") != "1":
+                raise RuntimeError("not run: validated on 2 GPUs; set SS_BENCH_TP_FUSED=1 to time it on more")
             fused_op = sharding.FusedTensorParallelProjection(shard.to(device), sharding.shard_columns(tp_n, world))
             for _ in range(3):
                 fused_op(tp_x)
