@@ -68,14 +68,49 @@ def peaks():
 
 
 class ClockSampler:
+    """SM clock and throttle reasons of one GPU sampled while the timed region runs: NVML queries
+    from a thread every 5 ms (read-only; the same counters `nvidia-smi --query-gpu=clocks.sm,
+    clocks_event_reasons.*` prints), or an `nvidia-smi -lms 100` loop when NVML cannot be bound."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+                   (0x4, "sw_power_cap"))
 
     def __init__(self, index):
         self.index, self.lines, self.proc = index, [], None
+        self.samples, self.stop, self.thread, self.nvml = [], threading.Event(), None, None
+
+    def _nvml_handle(self):
+        import pynvml
+        import torch
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+        uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except TypeError:
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        return pynvml, handle
+
+    def _poll(self, pynvml, handle):
+        top = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop.is_set():
+            self.samples.append((pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM), top,
+                                 int(reasons(handle))))
+            self.stop.wait(0.005)
 
     def __enter__(self):
+        try:
+            pynvml, handle = self._nvml_handle()
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:            # noqa: BLE001 - any NVML binding problem falls back to nvidia-smi
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
@@ -91,6 +126,10 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def __exit__(self, *exc):
+        self.stop.set()
+        if self.nvml is not None:
+            self.thread.join(timeout=2)
+            return
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -100,6 +139,13 @@ class ClockSampler:
 
     def summary(self):
         sm, mx, reasons = [], [], set()
+        if self.samples:
+            for clock, top, mask in self.samples:
+                sm.append(float(clock))
+                mx.append(float(top))
+                reasons.update(name for bit, name in self.REASON_BITS if mask & bit)
+            return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
+                        samples=len(sm), sm_min_mhz=min(sm), source="nvml")
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
