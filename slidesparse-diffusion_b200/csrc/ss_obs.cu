@@ -268,6 +268,7 @@ extern "C" int ss_obs_finish(const float* w, const float* scales, const uint8_t*
   SS_REQUIRE(mode_ok(group), SS_E_ARG, "obs_finish: group must be 4, 6 or 8");
   SS_REQUIRE(rows > 0 && rows < (1ll << 31) && columns > 0 && columns < (1ll << 31), SS_E_ARG, "obs_finish: invalid shape");
   const int64_t total = rows * ((columns + group - 1) / group);
+  SS_REQUIRE((total + 255) / 256 < (1ll << 31), SS_E_ARG, "obs_finish: weight too large for one launch");
   obs_finish_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       w, scales, zeros, static_cast<int>(rows), columns, group, check_grid, qweight, status);
   SS_CUDA(cudaGetLastError());
