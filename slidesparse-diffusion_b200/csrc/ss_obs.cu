@@ -46,7 +46,7 @@ obs_block_kernel(float* __restrict__ w, int rows, int64_t columns, int64_t start
                  uint8_t* __restrict__ zeros, float* __restrict__ errors, float* __restrict__ losses) {
   extern __shared__ __align__(16) unsigned char smem[];
   float* tri = reinterpret_cast<float*>(smem);
-  const int tri_size = width * (width + 1) / 2;
+  const int tri_size = (width * (width + 1) / 2 + 3) & ~3;      // keeps the rows behind it 16-byte aligned
   const int lane = threadIdx.x & 31, sl = lane & (kLanesPerRow - 1);
   const int slot = threadIdx.x / kLanesPerRow;
   float* open = tri + tri_size + slot * 2 * width;
@@ -100,7 +100,21 @@ obs_block_kernel(float* __restrict__ w, int rows, int64_t columns, int64_t start
       __syncwarp();
       if (sl == 0) { open[index] = fin; err[index] = e; }
       const float* frow = tri + off - index;       // frow[j] = factor[index][j] for j >= index
-      for (int j = index + 1 + sl; j < width; j += kLanesPerRow) open[j] = __fsub_rn(open[j], __fmul_rn(e, frow[j]));
+      if ((width & 3) == 0) {
+        // four columns per lane and step: one 16-byte read and write of the open values
+        float4* open4 = reinterpret_cast<float4*>(open);
+        for (int q4 = ((index + 1) >> 2) + sl; q4 < (width >> 2); q4 += kLanesPerRow) {
+          float4 o = open4[q4];
+          const int j = q4 << 2;
+          if (j > index) o.x = __fsub_rn(o.x, __fmul_rn(e, frow[j]));
+          if (j + 1 > index) o.y = __fsub_rn(o.y, __fmul_rn(e, frow[j + 1]));
+          if (j + 2 > index) o.z = __fsub_rn(o.z, __fmul_rn(e, frow[j + 2]));
+          o.w = __fsub_rn(o.w, __fmul_rn(e, frow[j + 3]));
+          open4[q4] = o;
+        }
+      } else {
+        for (int j = index + 1 + sl; j < width; j += kLanesPerRow) open[j] = __fsub_rn(open[j], __fmul_rn(e, frow[j]));
+      }
       __syncwarp();
       off += width - index;
     }
@@ -210,7 +224,8 @@ __global__ void obs_finish_kernel(const float* __restrict__ w, const float* __re
 using namespace ss;
 
 static size_t obs_block_smem(int64_t width) {
-  return static_cast<size_t>(width * (width + 1) / 2 + kRowsPerCta * 2 * width) * sizeof(float) + kRowsPerCta * width;
+  const int64_t triangle = (width * (width + 1) / 2 + 3) / 4 * 4;
+  return static_cast<size_t>(triangle + kRowsPerCta * 2 * width) * sizeof(float) + kRowsPerCta * width;
 }
 
 extern "C" int ss_obs_max_blocksize(void) {
