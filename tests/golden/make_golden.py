@@ -18,6 +18,7 @@ file.  Inputs are seeded numpy draws stored in the fixtures together with the ou
                    (the trailing update goes through the BLAS the reference was run with)
 """
 import argparse
+import os
 import importlib.util
 import sys
 from pathlib import Path
@@ -93,7 +94,7 @@ def structured_weight(rng, n, k, l, density=0.9):
 
 def main():
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE", "/root/reference"))
     args = parser.parse_args()
     ref = Path(args.reference)
     packing = load_file("ref_packing", ref / "sdacc/w8a8_slidesparse/packing.py")
