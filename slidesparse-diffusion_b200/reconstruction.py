@@ -28,16 +28,18 @@ def factor_hessian(hessian, damping=.01):
     decoupled, then the upper Cholesky factor of the inverse.  A Hessian that is not positive
     definite after damping fails in the factorisation; nothing is retried with more damping."""
     if hessian.ndim != 2 or hessian.shape[0] != hessian.shape[1]:
-        raise ValueError("Hessian must be square")
-    h = hessian.detach().float().clone()
-    if damping < 0 or not torch.isfinite(h).all():
-        raise ValueError("invalid Hessian or damping")
+        raise ValueError(f"the Hessian must be a square matrix, got {tuple(hessian.shape)}")
+    if damping < 0:
+        raise ValueError("damping must not be negative")
+    h = hessian.detach().to(torch.float32).clone()
+    if not bool(torch.isfinite(h).all()):
+        raise ValueError("the Hessian holds non-finite values")
     if not torch.allclose(h, h.T, rtol=1e-5, atol=1e-6):
-        raise ValueError("Hessian is not symmetric")
-    diagonal = h.diagonal()
+        raise ValueError("the Hessian is not symmetric")
+    diagonal = h.diagonal()                    # a view: the edits below land in h
     dead = diagonal == 0
-    if dead.any() and torch.count_nonzero(h[dead]):
-        raise ValueError("zero-diagonal Hessian has nonzero cross terms")
+    if bool(dead.any()) and int(torch.count_nonzero(h[dead])):
+        raise ValueError("an input with a zero diagonal entry has non-zero cross terms")
     diagonal[dead] = 1
     amount = damping * diagonal.mean()
     diagonal += amount
@@ -64,6 +66,38 @@ def max_blocksize():
     return int(backend.library().ss_obs_max_blocksize())
 
 
+def _check_compress_arguments(weight, curvature, group, method, blocksize, allow_tail):
+    """The reference's argument contract (`reconstruction.py:66-82` there): every violation is a
+    ValueError raised before any work is done.  Returns (rows, columns)."""
+    if group not in (4, 6, 8):
+        raise ValueError(f"sparsity group must be 4, 6 or 8, not {group!r}")
+    if method != "joint" and method != "prune_then_rtn":
+        raise ValueError(f"method must be 'joint' or 'prune_then_rtn', not {method!r}")
+    if blocksize < 1 or blocksize % group != 0:
+        raise ValueError(f"a column block of {blocksize} inputs would cut a group of {group}")
+    if weight.ndim != 2 or weight.numel() == 0:
+        raise ValueError("the weight must be a non-empty matrix [outputs, inputs]")
+    if not bool(torch.isfinite(weight).all()):
+        raise ValueError("the weight holds non-finite values")
+    rows, columns = weight.shape
+    if not allow_tail and columns % group != 0:
+        raise ValueError(f"{columns} inputs leave an incomplete group of {group}; pass allow_tail=True to accept it")
+    if tuple(curvature.upper.shape) != (columns, columns):
+        raise ValueError(f"the curvature factor is {tuple(curvature.upper.shape)}, the weight has {columns} inputs")
+    if curvature.upper.device != weight.device:
+        raise ValueError("the curvature factor and the weight are on different devices")
+    return rows, columns
+
+
+def _check_scales(scales, rows, device):
+    scales = scales.detach().float().clone()
+    if tuple(scales.shape) != (rows,) or scales.device != device:
+        raise ValueError(f"scales must be [{rows}] on the weight's device")
+    if not bool(torch.isfinite(scales).all()) or not bool((scales > 0).all()):
+        raise ValueError("scales must be finite and positive")
+    return scales
+
+
 @torch.inference_mode()
 def compress(weight, curvature, group, *, method="joint", blocksize=192, scales=None, allow_tail=False,
              progress=None):
@@ -72,22 +106,9 @@ def compress(weight, curvature, group, *, method="joint", blocksize=192, scales=
     row's INT8 grid as it is finalised.  Returns the reference's dictionary: qweight int8, scales,
     zeros (bool), compensated (fp32), proxy_loss [N], method, group, blocksize, weight_grid,
     curvature_damping, activation_error_compensated."""
-    if method not in ("joint", "prune_then_rtn") or group not in (4, 6, 8):
-        raise ValueError("unsupported method or sparsity group")
-    if blocksize <= 0 or blocksize % group:
-        raise ValueError("column block would split an N:M group")
-    if weight.ndim != 2 or not weight.numel() or not torch.isfinite(weight).all():
-        raise ValueError("invalid weight")
-    rows, columns = weight.shape
-    if columns % group and not allow_tail:
-        raise ValueError("full model groups required; tail handling is explicit")
-    if curvature.upper.shape != (columns, columns) or curvature.upper.device != weight.device:
-        raise ValueError("curvature input width/device mismatch")
+    rows, columns = _check_compress_arguments(weight, curvature, group, method, blocksize, allow_tail)
     if scales is not None:
-        scales = scales.detach().float().clone()
-        if (scales.shape != (rows,) or scales.device != weight.device
-                or not torch.isfinite(scales).all() or not (scales > 0).all()):
-            raise ValueError("invalid per-output-channel scales")
+        scales = _check_scales(scales, rows, weight.device)
     if not weight.is_cuda:
         raise ValueError("compress runs on the GPU only: move the weight and the curvature to a CUDA device")
     from . import backend
@@ -120,13 +141,14 @@ def compress(weight, curvature, group, *, method="joint", blocksize=192, scales=
         zeros[:, curvature.dead] = True
         backend.check(lib.ss_obs_finish(p(w), p(scales), p(zeros), rows, columns, group, int(joint),
                                         p(qweight), p(status), stream))
-    if not torch.isfinite(w).all() or not torch.isfinite(scales).all():
-        raise RuntimeError("nonfinite compensation")
+    # the reference's three post-conditions, each a RuntimeError
     flags = int(status.item())
+    if not bool(torch.isfinite(w).all()):
+        raise RuntimeError("the compensated weight holds non-finite values")
     if flags & 1:
-        raise RuntimeError("joint output left the frozen quantization grid")
+        raise RuntimeError("a jointly rounded weight is not on its row's INT8 grid")
     if flags & 2:
-        raise RuntimeError("structural sparsity violation")
+        raise RuntimeError("a complete group keeps more than group-2 non-zero weights")
     return dict(qweight=qweight, scales=scales, zeros=zeros, compensated=w, proxy_loss=losses, method=method,
                 group=group, blocksize=blocksize, weight_grid="signed[-128,127]; scale=2*Dense-row-absmax/255",
                 curvature_damping=curvature.damping, activation_error_compensated=False)
