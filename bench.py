@@ -430,6 +430,21 @@ def run_denoise(args, rank, world, local_rank):
         return float(t.item())
 
     steps = min(args.steps, spec.steps)
+    if args.variant != "all":
+        # one leg alone (for a launch list of exactly that variant): dense, or sparse with fused neighbours
+        if args.variant == "fused":
+            model.select(model.pack())
+            model.fuse_neighbours(True)
+        else:
+            model.select(0)
+        only = timed(denoiser.DenoiseLoop(model, graph=True, images=args.images), steps, args.warmup)
+        if rank == 0:
+            print(json.dumps({"metric": "denoise_step_ms", "value": only, "unit": "ms", "n_gpus": world,
+                              "steps": steps, "higher_is_better": False, "data": "synthetic",
+                              "config": {"workload": args.workload, "variant": args.variant, "blocks": spec.blocks}}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     model.select(0)
     dense_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
     dense_before = timed(dense_loop, steps, args.warmup)
@@ -496,6 +511,8 @@ def main():
                                  "sd35-large-512"))
     parser.add_argument("--images", type=int, default=1, help="images per forward in the denoise workloads")
     parser.add_argument("--blocks", type=int, default=None, help="override the block count (debug)")
+    parser.add_argument("--variant", default="all", choices=("all", "dense", "fused"),
+                        help="denoise workloads: time one leg alone (debug / profiling)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
