@@ -203,6 +203,26 @@ int ss_projection_peers(const void* x_bf16, int64_t x_row_stride, int64_t m, int
                         const void* const* destinations, int count, int64_t out_row_stride,
                         void* stream);
 
+/* Diagnostic.  No counterpart in the reference.  Runs the GEMM kernel itself (clusters of two CTAs,
+ * TMA producer, metadata copies, the real tile walk) on scratch operands of the given problem size
+ * and returns the cycles per pipeline stage (256 lifted columns = four tcgen05.mma.sp of the pair)
+ * that cluster 0 needed for its whole tile loop, with parts of the kernel switched off:
+ *   flags bit 0  no MMAs are issued (commits only): the shared-memory feed from L2 alone
+ *   flags bit 1  the epilogue hands every accumulator straight back: the main loop alone
+ * token_tile 0 lets the library choose (including the weights-resident form); 128 / 192 / 224 /
+ * 240 / 256 force a tile.  Allocates and frees its operands with cudaMalloc and synchronises the
+ * device.  This is how the ceiling of the main loop's dataflow is measured, as opposed to argued. */
+int ss_micro_pair_rate(int64_t m, int64_t n, int64_t pk, int token_tile, int flags,
+                       double* cycles_per_stage, int64_t* stages);
+
+/* Diagnostic.  No counterpart in the reference.  Proves the exit path of the bounded waits without
+ * starving a real kernel: one warp waits, for at most limit_ns (1 ns .. 100 ms), on an mbarrier
+ * that nothing arrives on.  The wait must run out, the kernel must return normally and leave the
+ * wait-limit bit (8) in the device status word, which the next ss_device_status reports (SS_E_DEVICE)
+ * and clears; the context stays usable.  *elapsed_ns = how long the kernel actually waited.
+ * Synchronises the device. */
+int ss_micro_wait_limit(int64_t limit_ns, int64_t* elapsed_ns);
+
 /* Diagnostic.  No counterpart in the reference.  Runs one CTA that issues `iterations` x 2
  * back-to-back tcgen05.mma instructions of 128 channels x token_tile tokens (sparse kind::i8 with
  * K = 64 lifted columns, or dense kind::i8 with K = 32) on operands that rotate through shared
@@ -224,6 +244,11 @@ int ss_micro_mma_rate(int token_tile, int sparse, int with_metadata_copy, int it
  *   - the first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current); make that first call before any
  *     stream capture begins;
+ *   - "allocates nothing" holds from the second call on: with CUDA's lazy module loading the
+ *     driver places the 32 MiB array and the two kernel images on the device when they are first
+ *     used.  A host that carves up all of HBM should therefore make one warm-up call per device and
+ *     per mode (or load with CUDA_MODULE_LOADING=EAGER) BEFORE it takes the memory, or that first
+ *     call can fail with SS_E_CUDA;
  *   - all calls on a device share the one array: two calls whose kernels may overlap on the
  *     GPU (different streams, or graphs launched concurrently) race on it -- serialise them;
  *   - the array keeps the previous call's contents; nothing needs clearing because the
@@ -235,7 +260,8 @@ int ss_projection_static(const void* x_bf16, int64_t x_row_stride, int64_t m, in
                          int64_t n, int64_t pn,
                          void* out_bf16, int64_t out_row_stride, void* stream);
 
-/* ---- prepared plans (resident scratch, cached tensor maps) ------------------------------- */
+/* ---- prepared plans (resident scratch; tensor maps come from the library's descriptor cache,
+ *      so a plan's weights and resident scratch are encoded once) ----------------------------- */
 
 /* Creates a plan for a fixed (m,k,n,group) on the current device; allocates its resident
  * q/sa scratch with cudaMalloc (the only allocating entry besides ss_plan_release's free).
@@ -267,9 +293,23 @@ int ss_gemm_resources(int64_t m, int64_t n, int64_t pk, int64_t* out, int n_out)
 
 /* ---- device status ------------------------------------------------------------------------ */
 
-/* Synchronises `stream` and returns (and clears) the device status word of the current device:
- * 0 = no kernel gave up on a bounded wait since the last read. */
+/* Synchronises `stream`, writes the device status word of the current device to *status and
+ * clears it.  0 = no kernel gave up on a bounded wait since the last read: returns SS_OK.
+ * Otherwise returns SS_E_DEVICE (bits: 1 TMA producer, 2 MMA issuer, 4 epilogue, 8 wait-limit
+ * probe); outputs of the launches since the previous check are then not to be trusted. */
 int ss_device_status(void* stream, int32_t* status);
+
+/* ---- tuning switches ----------------------------------------------------------------------- */
+
+/* The library reads its switches from the environment once, at first use (SS_TOKEN_TILE,
+ * SS_WIDE_CP, SS_META_WARP, SS_STORE, SS_RESIDENT, SS_PDL, SS_WAIT_NS); these two entries read and
+ * change them afterwards, for tests and measurements.  No counterpart in the reference.  Names:
+ * "token_tile" (0 = automatic, or 128/192/224/240/256), "wide_cp", "meta_warp" (-1 = automatic),
+ * "store" (1 = TMA-store epilogue), "resident" (weights-resident form), "pdl" (programmatic
+ * dependent launch), "wait_ns" (limit of every device-side wait, default 2e9).  Not synchronised
+ * with concurrent launches from other threads. */
+int ss_set_option(const char* name, int64_t value);
+int ss_get_option(const char* name, int64_t* value);
 
 #ifdef __cplusplus
 }

@@ -71,8 +71,11 @@ def load():
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE", "/root/reference"))
+    parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE"),
+                        help="root of the SlideSparse-Diffusion source tree (or set SS_REFERENCE)")
     parser.add_argument("--force", action="store_true")
     args = parser.parse_args()
+    if not args.reference:
+        parser.error("give --reference or set SS_REFERENCE")
     print(build(args.reference, args.force))
     sys.exit(0)

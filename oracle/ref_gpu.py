@@ -229,11 +229,14 @@ def time_reference():
 if __name__ == "__main__":
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("action", choices=("build", "generate", "time", "digest"))
-    parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE", "/root/reference"))
+    parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE"),
+                        help="root of the SlideSparse-Diffusion source tree (or set SS_REFERENCE)")
     parser.add_argument("--out", default=str(HERE.parent / "tests" / "golden" / "ref_gpu.npz"))
     parser.add_argument("--force", action="store_true")
     args = parser.parse_args()
     if args.action == "build":
+        if not args.reference:
+            parser.error("build needs --reference or SS_REFERENCE")
         print(build(args.reference, args.force))
     elif args.action == "time":
         time_reference()

@@ -115,6 +115,10 @@ def _declare(lib):
         "ss_gemm_resources": [i64, i64, i64, vp, i32],
         "ss_device_status": [vp, vp],
         "ss_micro_mma_rate": [i32, i32, i32, i32, vp],
+        "ss_micro_pair_rate": [i64, i64, i64, i32, i32, vp, vp],
+        "ss_micro_wait_limit": [i64, vp],
+        "ss_set_option": [c.c_char_p, i64],
+        "ss_get_option": [c.c_char_p, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -356,6 +360,36 @@ def micro_mma_rate(token_tile, sparse=True, with_metadata_copy=False, iterations
     return value.value
 
 
+def micro_pair_rate(m, n, pk, token_tile=0, no_mma=False, no_epilogue=False):
+    """(cycles per 256-column pipeline stage, stages) of cluster 0 of the real GEMM kernel on scratch
+    operands of this size, optionally without its MMAs and / or its epilogue work (diagnostic)."""
+    cycles, stages = ctypes.c_double(), ctypes.c_int64()
+    check(library().ss_micro_pair_rate(int(m), int(n), int(pk), int(token_tile), int(bool(no_mma)) | 2 * int(bool(no_epilogue)),
+                                       ctypes.byref(cycles), ctypes.byref(stages)))
+    return cycles.value, stages.value
+
+
+def micro_wait_limit(limit_ns):
+    """Nanoseconds a kernel really waited on a barrier nobody signals before its bounded wait gave
+    up; leaves the wait-limit bit in the device status word (diagnostic)."""
+    elapsed = ctypes.c_int64()
+    check(library().ss_micro_wait_limit(int(limit_ns), ctypes.byref(elapsed)))
+    return elapsed.value
+
+
+def set_option(name, value):
+    """Change a tuning switch of the native library (see ss_set_option); returns the previous value."""
+    previous = get_option(name)
+    check(library().ss_set_option(name.encode(), int(value)))
+    return previous
+
+
+def get_option(name):
+    value = ctypes.c_int64()
+    check(library().ss_get_option(name.encode(), ctypes.byref(value)))
+    return value.value
+
+
 PROLOGUES = {"none": 0, "norm_modulate": 1, "gelu": 2}
 
 
@@ -562,12 +596,22 @@ def _resources(handle):
 
 
 def device_status(device=None):
-    """Synchronise the current stream and return (and clear) the device's kernel status word."""
+    """Synchronise the current stream and return (and clear) the device's kernel status word:
+    0, or the bits of the bounded waits that ran out since the last call."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     status = ctypes.c_int32(0)
     with torch.cuda.device(device):
-        check(library().ss_device_status(_stream(device), ctypes.byref(status)))
+        rc = library().ss_device_status(_stream(device), ctypes.byref(status))
+    if rc != SS_E_DEVICE:
+        check(rc)
     return status.value
+
+
+def check_device(device=None):
+    """Raise RuntimeError if a kernel gave up on a bounded wait since the last check."""
+    status = device_status(device)
+    if status:
+        raise RuntimeError(f"a kernel gave up on a bounded wait (device status 0x{status:x})")
 
 
 # ------------------------------------------------------------------------------------------

@@ -1,7 +1,8 @@
 """Per-unit storage of the packed modes a denoiser switches between from step to step.
 
-Mirror of the reference's bank slots (`sdacc/diffusion_research/banks.py`: `ResidentBankSlot`
-:30-67, `arena_bytes` :69-71, `initial_residency_budget` :73-81, `coalesce_parameters` :106-127).
+Counterpart of the reference's bank slots (`sdacc/diffusion_research/banks.py`: `ResidentBankSlot`
+:30-67, `coalesce_parameters` :106-127); its memory-budget helpers for 40-80 GB parts (:69-81) have
+no use on a 180 GB GPU and are not carried.
 A unit (one routed projection group) has up to three prepared payloads, one per sparsity mode, each
 a dict of `packed`, `metadata`, `scales`, `bias`.  The operators are built over VIEWS of the slot's
 device buffers, and the kernels read those pointers at launch time, so a mode switch or an in-place
@@ -22,18 +23,24 @@ _DTYPES = {"packed": torch.int8, "metadata": torch.int32, "scales": torch.float3
 
 
 def _check_payloads(payloads):
-    if not payloads or any(type(mode) is not int or mode not in (4, 6, 8) for mode in payloads):
-        raise ValueError("frozen sparse modes required")
-    for values in payloads.values():
-        if set(values) != set(KEYS):
-            raise ValueError("complete packed payload required")
-        for key, value in values.items():
+    """A slot takes {4|6|8: {packed, metadata, scales, bias}} of contiguous CPU tensors."""
+    if not payloads:
+        raise ValueError("a bank slot needs at least one mode")
+    for mode, values in payloads.items():
+        if type(mode) is not int or mode not in (4, 6, 8):
+            raise ValueError(f"bank modes are the group sizes 4, 6 and 8, not {mode!r}")
+        missing, extra = set(KEYS) - set(values), set(values) - set(KEYS)
+        if missing or extra:
+            raise ValueError(f"mode {mode}: payload must hold exactly {KEYS} (missing {sorted(missing)}, extra {sorted(extra)})")
+        for key in KEYS:
+            value = values[key]
             if value.device.type != "cpu" or not value.is_contiguous():
-                raise ValueError("offline contiguous CPU payload required")
+                raise ValueError(f"mode {mode}: {key} must be a contiguous CPU tensor (payloads are staged from the host)")
             if value.dtype != _DTYPES[key]:
-                raise ValueError(f"{key} must be {_DTYPES[key]}")
-            if key in ("scales", "bias") and not torch.isfinite(value).all():
-                raise ValueError("finite FP32 scale/bias required")
+                raise ValueError(f"mode {mode}: {key} must be {_DTYPES[key]}, got {value.dtype}")
+        for key in ("scales", "bias"):
+            if not bool(torch.isfinite(values[key]).all()):
+                raise ValueError(f"mode {mode}: {key} holds a non-finite value")
 
 
 class ResidentBankSlot:
@@ -65,17 +72,20 @@ class ResidentBankSlot:
                 for key, value in self.views[mode].items():
                     self.buffers[(mode, key)] = value
         self.identity = dict(
-            frozen_payload_shapes={str(m): {k: list(v.shape) for k, v in row.items()} for m, row in self.host.items()},
-            GPU_persistent_bytes=sum(v.numel() * v.element_size() for v in self.buffers.values()),
-            host_pinned_when_CUDA=pin, residency=residency,
-            one_active_mode_per_unit=residency == "active",
-            all_transfers_require_timed_selector=residency == "active",
-            forward_disk_IO_or_packing=False)
+            payload_shapes={str(m): {k: list(v.shape) for k, v in row.items()} for m, row in self.host.items()},
+            device_bytes=self.device_bytes, pinned_host=pin, residency=residency,
+            copies_on_activate=residency == "active")
+
+    @property
+    def device_bytes(self):
+        """Bytes this slot keeps on the device: every mode ("all"), or per tensor kind the largest
+        mode ("active")."""
+        return sum(v.numel() * v.element_size() for v in self.buffers.values())
 
     def activate(self, mode, include_parameters=True):
         """Make `mode` the one whose operator may run; returns the bytes copied to the device."""
         if type(mode) is not int or mode not in self.host:
-            raise ValueError("unknown prepared bank mode")
+            raise ValueError(f"this slot holds modes {sorted(self.host)}, not {mode!r}")
         if mode == self.current_mode:
             return 0
         copied = 0
@@ -96,28 +106,6 @@ class ResidentBankSlot:
                 for mode, view in self.views.items()}
 
 
-def arena_bytes(payloads):
-    """Device bytes of an "active" slot: per tensor kind, the largest mode."""
-    if not payloads or any(set(row) != set(KEYS) for row in payloads.values()):
-        raise ValueError("all four active-slot tensors required")
-    return sum(max(row[key].numel() * row[key].element_size() for row in payloads.values()) for key in KEYS)
-
-
-def initial_residency_budget(slot_bytes, free_bytes, dense_peak_reserved, current_reserved,
-                             transient_lower_bound, safety_bytes=4 * 2 ** 30):
-    """Refuse to place slots that would not leave room for the dense model's measured peak."""
-    values = (slot_bytes, free_bytes, dense_peak_reserved, current_reserved, transient_lower_bound, safety_bytes)
-    if any(type(v) is not int or v < 0 for v in values):
-        raise ValueError("invalid measured residency components")
-    reserve = max(0, dense_peak_reserved - current_reserved)
-    required = slot_bytes + reserve + transient_lower_bound + safety_bytes
-    if required > free_bytes:
-        raise ValueError("active slots plus measured Dense workspace/margin exceed instantaneous free memory")
-    return dict(required_incremental_bytes=required, free_bytes=free_bytes, slot_tensor_bytes=slot_bytes,
-                measured_Dense_peak_extra_reserve_bytes=reserve, safety_bytes=safety_bytes,
-                Sparse_peak_measured=False, full_Sparse_memory_acceptance=False, required_H2D_must_be_timed=True)
-
-
 class CoefficientArena:
     """One FP32 device tensor holding scales|bias of many units back to back.
 
@@ -129,9 +117,9 @@ class CoefficientArena:
         for uid, slot in slots.items():
             n = widths[uid]
             if slot.residency != "active":
-                raise ValueError("a coefficient arena aliases modes: 'active' slots required")
+                raise ValueError("a coefficient arena makes the modes of a unit share one buffer: 'active' slots only")
             if any(row[key].numel() != n for row in slot.host.values() for key in ("scales", "bias")):
-                raise ValueError("coalesced parameters require the original output channels")
+                raise ValueError(f"unit {uid}: every mode needs {n} scales and {n} bias values")
             self.ranges[uid] = (size, n)
             size += 2 * n
         device = next(iter(slots.values())).device

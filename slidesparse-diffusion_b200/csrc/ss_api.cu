@@ -295,5 +295,51 @@ extern "C" int ss_device_status(void* stream, int32_t* status) {
   SS_CUDA(cudaMemcpy(&v, p, sizeof(v), cudaMemcpyDeviceToHost));
   if (v) SS_CUDA(cudaMemset(p, 0, sizeof(v)));
   *status = static_cast<int32_t>(v);
+  SS_REQUIRE(v == 0, SS_E_DEVICE,
+             "a kernel gave up on a bounded wait (status 0x%x:%s%s%s%s); results of the launches since the "
+             "last check are not to be trusted",
+             v, (v & kStatusProducerTimeout) ? " TMA producer" : "", (v & kStatusMmaTimeout) ? " MMA issuer" : "",
+             (v & kStatusEpilogueTimeout) ? " epilogue" : "", (v & kStatusProbeTimeout) ? " wait-limit probe" : "");
   return SS_OK;
+}
+
+namespace {
+struct OptionField { const char* name; int Options::*field; };
+const OptionField kOptionFields[] = {
+    {"token_tile", &Options::token_tile}, {"wide_cp", &Options::wide_cp}, {"meta_warp", &Options::meta_warp},
+    {"store", &Options::store},           {"resident", &Options::resident}, {"pdl", &Options::pdl},
+};
+}  // namespace
+
+extern "C" int ss_set_option(const char* name, int64_t value) {
+  SS_REQUIRE(name, SS_E_ARG, "set_option: name required");
+  Options& opt = options();
+  if (std::string(name) == "wait_ns") {
+    SS_REQUIRE(value > 0, SS_E_ARG, "set_option: wait_ns must be positive");
+    opt.wait_ns = static_cast<unsigned long long>(value);
+    return SS_OK;
+  }
+  for (const OptionField& f : kOptionFields)
+    if (std::string(name) == f.name) {
+      opt.*(f.field) = static_cast<int>(value);
+      return SS_OK;
+    }
+  set_error("set_option: unknown option '%s'", name);
+  return SS_E_ARG;
+}
+
+extern "C" int ss_get_option(const char* name, int64_t* value) {
+  SS_REQUIRE(name && value, SS_E_ARG, "get_option: name and value pointer required");
+  const Options& opt = options();
+  if (std::string(name) == "wait_ns") {
+    *value = static_cast<int64_t>(opt.wait_ns);
+    return SS_OK;
+  }
+  for (const OptionField& f : kOptionFields)
+    if (std::string(name) == f.name) {
+      *value = opt.*(f.field);
+      return SS_OK;
+    }
+  set_error("get_option: unknown option '%s'", name);
+  return SS_E_ARG;
 }

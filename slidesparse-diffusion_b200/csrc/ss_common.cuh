@@ -35,8 +35,38 @@ enum : uint32_t {
   kStatusProducerTimeout = 1u,
   kStatusMmaTimeout = 2u,
   kStatusEpilogueTimeout = 4u,
+  kStatusProbeTimeout = 8u,      // the wait-limit diagnostic (ss_micro_wait_limit)
 };
 uint32_t* device_status_ptr();   // address of the status word on the current device (or nullptr)
+constexpr unsigned long long kDefaultWaitNs = 2000000000ull;   // limit of every mbarrier wait
+
+// Tuning switches.  Read from the environment ONCE, when the library is first used (SS_TOKEN_TILE,
+// SS_WIDE_CP, SS_META_WARP, SS_STORE, SS_RESIDENT, SS_PDL, SS_WAIT_NS), and changeable afterwards
+// through ss_set_option; the launch path itself never calls getenv.
+struct Options {
+  int token_tile = 0;     // 0 = chosen per problem; 128 / 192 / 224 / 256 force a tile
+  int wide_cp = 1;        // one tcgen05.cp.128x256b per stage instead of two 128x128b
+  int meta_warp = -1;     // -1 = by pipeline depth; 0 / 1 force the metadata-copy warp off / on
+  int store = 1;          // 1 = TMA-store epilogue where alignment allows, 0 = direct stores
+  int resident = 1;       // weights-resident form where applicable
+  int pdl = 1;            // programmatic dependent launch between front-end and GEMM
+  unsigned long long wait_ns = kDefaultWaitNs;
+};
+Options& options();
+
+// cuTensorMapEncodeTiled behind a per-process cache keyed by everything the descriptor encodes
+// (address, type, extents, pitches, box, swizzle): a descriptor is pure geometry, so one built for
+// an address stays valid for as long as that geometry is wanted there.  Weights and the scratch of a
+// prepared plan hit the cache on every launch after the first.
+struct MapKey {
+  const void* base;
+  int type, rank, swizzle;
+  unsigned long long dims[3], strides[2];
+  unsigned box[3];
+};
+int encode_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base,
+               const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
+               CUtensorMapSwizzle swizzle);
 
 // ---- entry points implemented per kernel file -------------------------------------------
 int launch_quantize_lift(const void* x, int64_t sx, int64_t m, int64_t k, int group,
@@ -72,6 +102,11 @@ struct GemmArgs {
   // first column) instead of `out`; all share out_stride
   const void* peer_out[8] = {};
   int peer_count = 0;
+  // diagnostics (ss_micro.cu): wait limit of this launch (0 = the library's), kernel parts switched
+  // off (bit 0 the MMAs, bit 1 the epilogue work), and where cluster 0 reports {cycles, stages}
+  unsigned long long wait_ns = 0;
+  int debug = 0;
+  unsigned long long* probe = nullptr;
 };
 constexpr int kMaxPeers = 8;
 struct GemmResources {
@@ -131,15 +166,17 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after about two seconds of wall time and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: gives up after limit_ns of wall time (two seconds unless the launch says
+// otherwise) and returns false.  The clock is looked at every 64 polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          unsigned long long limit_ns = kDefaultWaitNs) {
   if (mbar_test(bar, parity)) return true;
   uint64_t deadline = 0;
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_test(bar, parity)) return true;
-    if ((spin & 0x3ffu) == 0) {
+    if ((spin & 0x3fu) == 0) {
       uint64_t now = globaltimer_ns();
-      if (deadline == 0) deadline = now + 2000000000ull;
+      if (deadline == 0) deadline = now + limit_ns;
       else if (now > deadline) return false;
     }
   }

@@ -31,6 +31,29 @@ constexpr int kPairSub = kPairEpiWarps / 4;            // warps sharing a quadra
 // stages (token tiles up to 224: -6 % on 4096x3072->9216) and costs with three (256).
 constexpr int kPairThreads = 64 + 32 * kPairEpiWarps + 32;
 
+// Per-tile time stamps of the three roles of each cluster's rank-0 CTA, for builds made with
+// -DSS_TIMELINE only (a development aid; the shipped library does not contain it).
+#ifdef SS_TIMELINE
+constexpr int kTlTiles = 32, kTlSlots = 4, kTlClusters = 80;
+__device__ long long g_timeline[kTlClusters * 3 * kTlTiles * kTlSlots];
+#define SS_TL(role, tile_index, slot)                                                          \
+  do {                                                                                         \
+    if (rank == 0 && pair < kTlClusters && (tile_index) < kTlTiles)                            \
+      g_timeline[((pair * 3 + (role)) * kTlTiles + (tile_index)) * kTlSlots + (slot)] = clock64(); \
+  } while (0)
+// per-cluster sums of the cycles the producer and the MMA thread spend in each kind of operation
+constexpr int kPfSlots = 16;
+__device__ long long g_profile[kTlClusters * kPfSlots];
+#define SS_PF_BEGIN() long long pf_t = clock64()
+#define SS_PF(acc) do { const long long pf_n = clock64(); (acc) += pf_n - pf_t; pf_t = pf_n; } while (0)
+#define SS_PF_STORE(slot, value) do { if (rank == 0 && pair < kTlClusters) g_profile[pair * kPfSlots + (slot)] = (value); } while (0)
+#else
+#define SS_TL(role, tile_index, slot) do {} while (0)
+#define SS_PF_BEGIN() do {} while (0)
+#define SS_PF(acc) do {} while (0)
+#define SS_PF_STORE(slot, value) do {} while (0)
+#endif
+
 template <int NT, int KB>
 struct PairTile {
   static constexpr int kHalf = NT / 2;                             // B token rows held per CTA
@@ -40,9 +63,9 @@ struct PairTile {
   static constexpr int kEBlock = kTileCh * kBlockK / 8;
   static constexpr int kEBytes = kEBlock * KB;
   static constexpr int kStageBytes = kABytes + kBBytes + kEBytes;  // per CTA
-  static constexpr int kSaBytes = kPairEpiWarps * NT * 4;           // token scales, one copy per warp
   static constexpr int kStoreTile = 32 * 32 * 2;                    // 32 tokens x 32 channels BF16
-  static constexpr int kFixed = kSaBytes + 256 + 1024;              // + barrier block + alignment slack
+  static constexpr int kBarBytes = 512;                             // barrier block
+  static constexpr int kFixed = kBarBytes + 1024;                   // barrier block + alignment slack
   static constexpr int kBudget = 227 * 1024 - kFixed;
   // two staging tiles per epilogue warp if at least four pipeline stages still fit, else one
   static constexpr int kStages2 = (kBudget - 2 * kPairEpiWarps * kStoreTile) / kStageBytes;
@@ -56,14 +79,16 @@ struct PairTile {
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + kStages * kABytes;
   static constexpr int kOffE = kOffB + kStages * kBBytes;
-  static constexpr int kOffSa = kOffE + kStages * kEBytes;
-  static constexpr int kOffStore = kOffSa + kSaBytes;               // BF16 staging for TMA stores
+  static constexpr int kOffStore = kOffE + kStages * kEBytes;       // BF16 staging for TMA stores
   static constexpr int kOffBar = kOffStore + kStoreBufs * kPairEpiWarps * kStoreTile;
-  static constexpr int kSmemBytes = kOffBar + 256 + 1024;
+  static constexpr int kSmemBytes = kOffBar + kBarBytes + 1024;
   static_assert(kStages >= 2, "pipeline depth");
   static_assert(kMetaCol + kStages * kMetaColsPerStage <= kTmemCols, "TMEM budget");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
-  static_assert(NT % 32 == 0 && NT >= 64 && NT <= 256, "token tile of a CTA pair");
+  static_assert(NT % 16 == 0 && NT >= 64 && NT <= 256, "token tile of a CTA pair");
+  // chunks of 32 tokens the epilogue walks; a tile of 240 ends in a half chunk of 16 tokens
+  static constexpr int kChunks = (NT + 31) / 32;
+  static constexpr bool kHalfTail = NT % 32 != 0;
   static_assert(kBBlock % 1024 == 0, "B blocks must keep the 128B-swizzle alignment");
 };
 
@@ -88,14 +113,16 @@ template <int NT, int KB>
 struct PairResident {
   using T = PairTile<NT, KB>;
   static constexpr int kMaxStagesK = (kTmemCols - 2 * NT) / T::kMetaColsPerStage;   // TMEM left for metadata
-  static constexpr int kFixed = T::kSaBytes + kPairEpiWarps * T::kStoreTile + 256 + 1024;
-  // B pipeline stages that fit next to `slabs` resident A slabs (0 if fewer than 3)
+  static constexpr int kStoreBufs = 2;                              // staging tiles per epilogue warp
+  static constexpr int kFixed = kStoreBufs * kPairEpiWarps * T::kStoreTile + T::kBarBytes + 1024;
+  // kStages if that many B pipeline stages fit next to `slabs` resident A slabs, else 0
   static int b_stages(int slabs) {
     const int room = 227 * 1024 - kFixed - slabs * T::kABytes;
     const int stages = room / T::kBBytes;
-    return stages < 3 ? 0 : (stages > 8 ? 8 : stages);
+    return stages < kStages ? 0 : kStages;
   }
-  static int smem_bytes(int slabs, int stages) { return slabs * T::kABytes + stages * T::kBBytes + kFixed; }
+  static constexpr int kStages = 4;     // activation stages of the resident form (the MMA loop is unrolled over them)
+  static int smem_bytes(int slabs) { return slabs * T::kABytes + kStages * T::kBBytes + kFixed; }
 };
 
 template <int NT, int KB, int MODE, bool RES = false, class Peers = NoPeers>
@@ -103,7 +130,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_e,
-                        const __grid_constant__ CUtensorMap map_out, const KernelArgs args,
+                        const __grid_constant__ CUtensorMap map_out,
+                        const __grid_constant__ CUtensorMap map_out_tail, const KernelArgs args,
                         const __grid_constant__ Peers peers) {
   using T = PairTile<NT, KB>;
   constexpr bool INT32_OUT = MODE == kOutInt32, HAS_ADDEND = MODE == kOutBf16Addend;
@@ -113,13 +141,14 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const int num_st = (args.num_kb + KB - 1) / KB;
   // pipeline depth and region offsets: compile-time in the streaming form, from the K extent in
   // the resident form (A slabs first, then the B stages, which also stage the metadata once)
-  const int stages = RES ? args.res_stages : T::kStages;
+  // pipeline depth: what fits in the streaming form, four activation stages in the resident form
+  constexpr int kRing = RES ? PairResident<NT, KB>::kStages : T::kStages;
+  constexpr int stages = kRing;
   const int off_a = 0;
   const int off_b = RES ? num_st * T::kABytes : T::kOffB;
   const int off_e = RES ? off_b : T::kOffE;
-  const int off_sa = RES ? off_b + stages * T::kBBytes : T::kOffSa;
-  const int off_store = off_sa + T::kSaBytes;
-  constexpr int kStoreBufs = RES ? 1 : T::kStoreBufs;
+  const int off_store = RES ? off_b + stages * T::kBBytes : T::kOffStore;
+  constexpr int kStoreBufs = RES ? PairResident<NT, KB>::kStoreBufs : T::kStoreBufs;
   const int off_bar = off_store + kStoreBufs * kPairEpiWarps * T::kStoreTile;
   constexpr int kBarStride = RES ? 8 : T::kStages;
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + off_bar);
@@ -129,8 +158,13 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   // streaming form: metadata of a stage is in TMEM (rank 0).  Resident form: [0] metadata of the
   // whole K extent is in TMEM (both CTAs), [1] resident operands have landed (rank 0)
   uint64_t* bar_meta = bar_acc_empty + T::kAccBufs;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meta + kBarStride);
+  // streaming form: the metadata of a stage has landed in shared memory (rank 0).  It has a barrier
+  // of its own so that its copy into TMEM runs while the stage's weights and activations still land.
+  uint64_t* bar_e = bar_meta + kBarStride;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_e + kBarStride);
+  static_assert((5 * kBarStride + 2 * T::kAccBufs) * 8 + 8 <= T::kBarBytes, "barrier block");
   static_assert(!RES || T::kAccBufs == 2, "resident form assumes two accumulators");
+  static_assert(!(T::kHalfTail && MODE == kOutBf16TmaPeers), "the tensor-parallel stores take whole chunks only");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -148,6 +182,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       ptx::mbar_init(&bar_full[s], 1);
       ptx::mbar_init(&bar_empty[s], 1);
       ptx::mbar_init(&bar_meta[s], 1);
+      ptx::mbar_init(&bar_e[s], 1);
     }
     for (int b = 0; b < T::kAccBufs; ++b) {
       ptx::mbar_init(&bar_acc_full[b], 1);
@@ -157,7 +192,10 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
     ptx::prefetch_tensormap(&map_e);
-    if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) ptx::prefetch_tensormap(&map_out);
+    if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) {
+      ptx::prefetch_tensormap(&map_out);
+      if constexpr (T::kHalfTail) ptx::prefetch_tensormap(&map_out_tail);
+    }
     if constexpr (MODE == kOutBf16TmaPeers) {
       for (int g = 0; g < args.peer_count; ++g) ptx::prefetch_tensormap(&peers.m[g]);
     }
@@ -174,64 +212,118 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
+    // Three instructions per stage: the metadata and the activations as 3-D boxes whose outermost
+    // coordinate is the block of 128 lifted columns (so that both blocks of a stage land back to
+    // back), the weights as a box of both blocks side by side.  A box that reaches past the last
+    // block is filled with zeros and still counts its full size on the barrier, so every stage
+    // expects the same byte count.  Issuing a TMA instruction costs a thread 60 to 100 cycles, and
+    // three lanes issuing one each in the same warp instruction cost the same as one lane issuing
+    // three, so the count per stage is what matters: with five (one per 128-column block and
+    // operand) this thread set the pace of the whole pipeline.
     if (lane == 0) {
       uint32_t s = 0, phase = 0;       // pipeline stage and the parity of its current use
+      uint32_t issued = 0, tl = 0;     // stages filled so far
       bool ok = true;
+      long long pf_wait = 0, pf_arm = 0, pf_a = 0, pf_b = 0, pf_e = 0;
+      (void)pf_wait; (void)pf_arm; (void)pf_a; (void)pf_b; (void)pf_e;
+      constexpr uint32_t kStageTx = 2u * (RES ? T::kBBytes : T::kABytes + T::kBBytes);   // both CTAs' bytes
       if constexpr (RES) {
         // the weights do not depend on the preceding kernel: fetch the resident operands first
         if (tile_first < num_tiles) {
           const int ch0 = (tile_first % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
-          if (rank == 0)
-            ptx::mbar_arrive_expect_tx(&bar_meta[1], 2 * (num_st * T::kABytes + args.num_kb * T::kEBlock));
-          for (int st = 0; st < num_st; ++st)
+          if (rank == 0) ptx::mbar_arrive_expect_tx(&bar_meta[1], 2 * num_st * (T::kABytes + T::kEBytes));
+          for (int st = 0; st < num_st; ++st) {
             ptx::tma_load_2d_pair(smem + off_a + st * T::kABytes, &map_a, &bar_meta[1], st * KB * (kBlockK / 2), ch0);
-          for (int kb = 0; kb < args.num_kb; ++kb)
-            ptx::tma_load_3d_pair(smem + off_e + kb * T::kEBlock, &map_e, &bar_meta[1], 0, kb, ch0 >> 5);
-          // the metadata is staged where the first activation stages will live
-          if (!ptx::mbar_wait(&bar_meta[0], 0)) ok = false;
+            // the metadata is staged where the first activation stages will live
+            ptx::tma_load_3d_pair(smem + off_e + st * T::kEBytes, &map_e, &bar_meta[1], 0, ch0 >> 5, st * KB);
+          }
+          if (!ptx::mbar_wait(&bar_meta[0], 0, args.wait_ns)) ok = false;
         }
       }
       ptx::grid_dep_wait();           // q is written by the kernel launched just before this one
-      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step) {
+      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++tl) {
         const int ch0 = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
         const int tok0 = (tile / tiles_ch2) * NT + static_cast<int>(rank) * T::kHalf;
+        SS_TL(0, tl, 0);
         for (int st = 0; st < num_st; ++st) {
-          const int kb0 = st * KB;
-          const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
-          if (!ptx::mbar_wait(&bar_empty[s], phase ^ 1u)) { ok = false; break; }
-          if constexpr (RES) {
-            if (rank == 0) ptx::mbar_arrive_expect_tx(&bar_full[s], 2 * nkb * T::kBBlock);
-          } else {
-            if (rank == 0)
-              ptx::mbar_arrive_expect_tx(&bar_full[s], 2 * (T::kABytes + nkb * (T::kBBlock + T::kEBlock)));
-            ptx::tma_load_2d_pair(smem + off_a + s * T::kABytes, &map_a, &bar_full[s], kb0 * (kBlockK / 2), ch0);
+          SS_PF_BEGIN();
+          if (!ptx::mbar_wait(&bar_empty[s], phase ^ 1u, args.wait_ns)) { ok = false; break; }
+          SS_PF(pf_wait);
+          if (rank == 0) {
+            if constexpr (!RES) ptx::mbar_arrive_expect_tx(&bar_e[s], 2u * T::kEBytes);
+            ptx::mbar_arrive_expect_tx(&bar_full[s], kStageTx);
           }
-          for (int h = 0; h < nkb; ++h) {
-            ptx::tma_load_2d_pair(smem + off_b + s * T::kBBytes + h * T::kBBlock, &map_b, &bar_full[s],
-                                  (kb0 + h) * kBlockK, tok0);
-            if constexpr (!RES)
-              ptx::tma_load_3d_pair(smem + off_e + s * T::kEBytes + h * T::kEBlock, &map_e, &bar_full[s], 0,
-                                    kb0 + h, ch0 >> 5);
+          SS_PF(pf_arm);
+          if constexpr (!RES) {
+            // the metadata first: it is small, and its copy into TMEM can start while the rest lands
+            ptx::tma_load_3d_pair(smem + off_e + s * T::kEBytes, &map_e, &bar_e[s], 0, ch0 >> 5, st * KB);
+            SS_PF(pf_e);
           }
-          if (++s == static_cast<uint32_t>(stages)) { s = 0; phase ^= 1u; }
+          ptx::tma_load_3d_pair(smem + off_b + s * T::kBBytes, &map_b, &bar_full[s], 0, tok0, st * KB);
+          SS_PF(pf_b);
+          if constexpr (!RES) {
+            ptx::tma_load_2d_pair(smem + off_a + s * T::kABytes, &map_a, &bar_full[s], st * KB * (kBlockK / 2), ch0);
+            SS_PF(pf_a);
+          }
+          if (++s == static_cast<uint32_t>(kRing)) { s = 0; phase ^= 1u; }
+          ++issued;
+        }
+        SS_TL(0, tl, 1);
+      }
+      SS_PF_STORE(0, pf_wait); SS_PF_STORE(1, pf_arm); SS_PF_STORE(2, pf_a); SS_PF_STORE(3, pf_b); SS_PF_STORE(4, pf_e);
+      SS_PF_STORE(5, static_cast<long long>(issued));
+      if (!ok) {
+        atomicOr(args.status, kStatusProducerTimeout);
+        // Let the copies already in flight land before the pair's shared memory is released.  The
+        // full barriers live in rank 0 and count both CTAs' bytes, so rank 0 waits (bounded) for the
+        // last fill of every stage that was filled; rank 1 is held by the cluster barrier at the end
+        // of the kernel, which rank 0 reaches only after this loop.
+        if (rank == 0) {
+          const unsigned long long limit = args.wait_ns / 8 + 1;
+          if constexpr (RES) ptx::mbar_wait(&bar_meta[1], 0, limit);
+          for (uint32_t f = 0; f < static_cast<uint32_t>(kRing) && f < issued; ++f) {
+            const uint32_t fills = (issued - f + kRing - 1) / kRing;
+            ptx::mbar_wait(&bar_full[f], (fills - 1) & 1u, limit);
+            if constexpr (!RES) ptx::mbar_wait(&bar_e[f], (fills - 1) & 1u, limit);
+          }
         }
       }
-      if (!ok) atomicOr(args.status, kStatusProducerTimeout);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (rank 0 only)
+    // The tensor pipe queues next to nothing: an MMA is accepted when the one before it is nearly
+    // done, so whatever else this thread executes between two MMAs (address arithmetic, barrier
+    // polls, commits) is time the pipe stands idle.  The ring is therefore unrolled with the stage
+    // slot as a compile-time constant: every shared-memory descriptor is one add away from a
+    // value computed before the loop, and a stage costs four MMAs, one commit and one barrier poll.
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = (1u << 2) | (2u << 4) | (1u << 7) | (1u << 10) |
                                  (static_cast<uint32_t>(NT >> 3) << 17) |
                                  (static_cast<uint32_t>((2 * kTileCh) >> 4) << 24);
       constexpr uint32_t a_layout = KB == 2 ? 2u : 4u, a_sbo = KB == 2 ? 1024u : 512u;
-      uint32_t s = 0, phase = 0, acc_it = 0;     // pipeline stage and the parity of its current use
+      // descriptor = {low word: address / 16 | leading offset (16 B) / 16 << 16, high word: constant}
+      constexpr uint32_t kDescHiA = (a_sbo >> 4) | (1u << 14) | (a_layout << 29);
+      constexpr uint32_t kDescHiB = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t a_lo0 = ((ptx::smem_u32(smem + off_a) & 0x3ffffu) >> 4) | (1u << 16);
+      const uint32_t b_lo0 = ((ptx::smem_u32(smem + off_b) & 0x3ffffu) >> 4) | (1u << 16);
+      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+      const bool odd_tail = (args.num_kb % KB) != 0;       // the last stage of a tile holds one block only
+      uint32_t phase = 0, acc_it = 0;
       bool ok = true, ready = false;
-      int release_stage = -1;        // stage whose MMAs are issued but whose barrier is not yet committed
+      // diagnostics (ss_micro_pair_rate): cluster 0 reports the cycles its tile loop took; bit 0 of
+      // args.debug leaves the MMAs out (commits only), so that the operand feed is timed alone
+      const bool probe = args.probe != nullptr && pair == 0;
+      const bool issue_mma = (args.debug & 1) == 0;
+      long long probe_begin = 0;
+      uint32_t probe_stages = 0, last_buf = 0, last_use = 0, tl = 0;
+      long long pf_acc = 0, pf_ready = 0, pf_mma = 0, pf_commit = 0, pf_peek = 0;
+      (void)pf_acc; (void)pf_ready; (void)pf_mma; (void)pf_commit; (void)pf_peek;
+      int tile = tile_first;
+      bool more = tile < num_tiles;
       if constexpr (RES) {
         // once per cluster: metadata of the whole K extent from its staging area into TMEM
-        if (tile_first < num_tiles) {
-          if (!ptx::mbar_wait(&bar_meta[1], 0)) ok = false;
+        if (more) {
+          if (!ptx::mbar_wait(&bar_meta[1], 0, args.wait_ns)) ok = false;
           ptx::tc_fence_after();
           const uint32_t e_addr = ptx::smem_u32(smem + off_e);
           const uint32_t e_tmem = tmem_base + T::kMetaCol;
@@ -245,58 +337,96 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           ptx::tc_commit_pair(&bar_meta[0], 3);       // both producers: the staging area is free
         }
       }
-      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it) {
-        const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
-        if (!ptx::mbar_wait(&bar_acc_empty[buf], (acc_use & 1u) ^ 1u)) { ok = false; break; }
+      if (probe) probe_begin = clock64();
+      int st = 0;
+      uint32_t buf = 0, d_tmem = tmem_base;
+      if (more && ok) {
+        SS_TL(1, tl, 0);
+        if (!ptx::mbar_wait(&bar_acc_empty[0], 1u, args.wait_ns)) ok = false;
+        SS_TL(1, tl, 1);
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * NT;
-        for (int st = 0; st < num_st; ++st) {
-          const int kb0 = st * KB;
-          const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
-          // with a metadata warp the stage is ready when its metadata copy has completed (which
-          // implies that the operands have landed); without one this thread copies it itself
-          uint64_t* bar_ready = meta_warp ? bar_meta : bar_full;
-          if (!ready && !ptx::mbar_wait(&bar_ready[s], phase)) { ok = false; break; }
+      }
+      while (more && ok) {
+#pragma unroll
+        for (int slot = 0; slot < kRing; ++slot) {
+          SS_PF_BEGIN();
+          if (!ready && !ptx::mbar_wait(&bar_full[slot], phase, args.wait_ns)) { ok = false; more = false; break; }
+          // the stage's metadata: copied into TMEM by the metadata warp (done long before the operands
+          // have landed), or still to be copied by this thread
+          if constexpr (!RES) {
+            if (!ptx::mbar_wait(meta_warp ? &bar_meta[slot] : &bar_e[slot], phase, args.wait_ns)) { ok = false; more = false; break; }
+          }
+          SS_PF(pf_ready);
+          if (st == 0) SS_TL(1, tl, 2);
+          ++probe_stages;
           ptx::tc_fence_after();
-          // resident form: weights and metadata are indexed by the K position, not by the stage
-          const uint32_t a_addr = ptx::smem_u32(smem + off_a + (RES ? st : static_cast<int>(s)) * T::kABytes);
-          const uint32_t b_addr = ptx::smem_u32(smem + off_b + s * T::kBBytes);
-          const uint32_t e_tmem = tmem_base + T::kMetaCol + (RES ? st : static_cast<int>(s)) * T::kMetaColsPerStage;
+          // resident form: weights and metadata are indexed by the K position, not by the ring slot
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(RES ? st : slot) * (T::kABytes >> 4);
+          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(slot) * (T::kBBytes >> 4);
+          const uint32_t e_tmem = tmem_base + T::kMetaCol + static_cast<uint32_t>(RES ? st : slot) * T::kMetaColsPerStage;
+          const bool full_stage = !(odd_tail && st == num_st - 1);
           if (!RES && !meta_warp) {
-            const uint32_t e_addr = ptx::smem_u32(smem + off_e + s * T::kEBytes);
-            if (KB == 2 && nkb == 2 && args.wide_cp) {
+            // no metadata warp (three pipeline stages): this thread copies the stage's metadata itself
+            const uint32_t e_addr = ptx::smem_u32(smem + off_e) + slot * T::kEBytes;
+            if (KB == 2 && full_stage && args.wide_cp) {
               // both metadata blocks of the stage in one instruction: block h is the h-th 16-byte
               // column of a 128 x 32-byte matrix whose columns lie kEBlock bytes apart
               ptx::tc_cp_128x256b_pair(e_tmem, smem_desc(e_addr, T::kEBlock, 128, 0));
             } else {
-              for (int h = 0; h < nkb; ++h)
+              for (int h = 0; h < (full_stage ? KB : 1); ++h)
                 ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
             }
           }
-          const uint32_t s_next = s + 1 == static_cast<uint32_t>(stages) ? 0u : s + 1;
-          const uint32_t phase_next = s_next == 0u ? phase ^ 1u : phase;
-          for (int j = 0; j < 2 * nkb; ++j) {
-            const uint64_t adesc = smem_desc(a_addr + j * 32, 16, a_sbo, a_layout);
-            const uint64_t bdesc = smem_desc(b_addr + (j >> 1) * T::kBBlock + (j & 1) * 64, 16, 1024, 2);
-            ptx::tc_mma_sp_i8_pair(d_tmem, adesc, bdesc, e_tmem + j * 2, idesc, (st | j) != 0 ? 1u : 0u);
-            if (j == 0 && release_stage >= 0) {
-              // the previous stage is handed back while this stage's first MMA keeps the pipe busy
-              ptx::tc_commit_pair(&bar_empty[release_stage], 3);
-              release_stage = -1;
+          // K = 64 lifted columns per instruction: 32 B of compressed weights, 64 B of activations per row
+          if (issue_mma) {
+            ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo, kDescHiA), desc(b_lo, kDescHiB), e_tmem, idesc, st != 0 ? 1u : 0u);
+            ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo + 2, kDescHiA), desc(b_lo + 4, kDescHiB), e_tmem + 2, idesc, 1u);
+            if (KB == 2 && full_stage) {
+              ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo + 4, kDescHiA), desc(b_lo + (T::kBBlock >> 4), kDescHiB), e_tmem + 4, idesc, 1u);
+              ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo + 6, kDescHiA), desc(b_lo + (T::kBBlock >> 4) + 4, kDescHiB), e_tmem + 6, idesc, 1u);
             }
           }
-          release_stage = static_cast<int>(s);
+          SS_PF(pf_mma);
+          // The stage goes back to the producers as soon as its MMAs are queued (the arrival happens
+          // when they have completed): the MMAs queue ahead of the pipe, so the commit costs this
+          // thread time the pipe does not wait for, and the refill is not held up by the next
+          // stage's arrival.
+          ptx::tc_commit_pair(&bar_empty[slot], 3);
+          SS_PF(pf_commit);
           // a look at the next stage's barrier once this stage's work is queued: it has usually
           // completed by now, and a successful look is far cheaper than a wait
-          ready = mbar_peek(&bar_ready[s_next], phase_next);
-          s = s_next;
-          phase = phase_next;
+          ready = mbar_peek(&bar_full[(slot + 1) % kRing], slot == kRing - 1 ? phase ^ 1u : phase);
+          if (slot == kRing - 1) phase ^= 1u;
+          SS_PF(pf_peek);
+          if (++st == num_st) {
+            // the tile is complete: publish the accumulator
+            ptx::tc_commit_pair(&bar_acc_full[buf], 3);
+            SS_PF(pf_commit);
+            SS_TL(1, tl, 3);
+            last_buf = buf;
+            last_use = acc_it / T::kAccBufs;
+            st = 0;
+            tile += tile_step;
+            ++acc_it;
+            ++tl;
+            if (tile >= num_tiles) { more = false; break; }
+            buf = acc_it % T::kAccBufs;
+            d_tmem = tmem_base + buf * NT;
+            SS_TL(1, tl, 0);
+            if (!ptx::mbar_wait(&bar_acc_empty[buf], ((acc_it / T::kAccBufs) & 1u) ^ 1u, args.wait_ns)) { ok = false; more = false; break; }
+            SS_PF(pf_acc);
+            SS_TL(1, tl, 1);
+            ptx::tc_fence_after();
+          }
         }
-        if (release_stage >= 0) {
-          ptx::tc_commit_pair(&bar_empty[release_stage], 3);
-          release_stage = -1;
-        }
-        if (ok) ptx::tc_commit_pair(&bar_acc_full[buf], 3);
+      }
+      SS_PF_STORE(8, pf_acc); SS_PF_STORE(9, pf_ready); SS_PF_STORE(10, pf_mma); SS_PF_STORE(11, pf_commit);
+      SS_PF_STORE(12, pf_peek); SS_PF_STORE(13, static_cast<long long>(probe_stages));
+      if (probe && ok && probe_stages > 0) {
+        // the last tile's accumulator is complete when its barrier (this CTA's copy) flips
+        if (!ptx::mbar_wait(&bar_acc_full[last_buf], last_use & 1u, args.wait_ns)) ok = false;
+        args.probe[0] = static_cast<unsigned long long>(clock64() - probe_begin);
+        args.probe[1] = probe_stages;
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
     }
@@ -311,7 +441,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
           // the stage's previous metadata is no longer read once its MMAs have completed, which
           // the producer has already waited for before refilling the stage
-          if (!ptx::mbar_wait(&bar_full[s], phase)) { ok = false; break; }
+          if (!ptx::mbar_wait(&bar_e[s], phase, args.wait_ns)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t e_addr = ptx::smem_u32(smem + off_e + s * T::kEBytes);
           const uint32_t e_tmem = tmem_base + T::kMetaCol + s * T::kMetaColsPerStage;
@@ -324,7 +454,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
           }
           ptx::tc_commit_pair(&bar_meta[s], 1);      // arrives (rank 0 only) when the copy has completed
-          if (++s == static_cast<uint32_t>(stages)) { s = 0; phase ^= 1u; }
+          if (++s == static_cast<uint32_t>(kRing)) { s = 0; phase ^= 1u; }
         }
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
@@ -337,21 +467,23 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // tokens of one channel per register pair, which is exactly what stmatrix.trans needs to
     // write 8 tokens x 8 channels blocks token-major: two values are converted with one packed
     // BF16 conversion and 32 of them stored with one stmatrix.x4.
+    // Token scales never touch shared memory: lane l keeps the scale of token l of each of the
+    // warp's chunks in a register (fetched one tile ahead) and the lanes exchange them by shuffle.
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
-    float* sa_s = reinterpret_cast<float*>(smem + off_sa) + (warp - 2) * NT;
+    const int half = (warp - 2) >> 2;             // this warp takes chunks half, half + kPairSub, ...
     const int lane_ch = lane >> 2, tpair = (lane & 3) * 2;
-    uint32_t acc_it = 0, store_it = 0;
+    uint32_t acc_it = 0, store_it = 0, tl = 0;
     bool ok = true;
-    constexpr int kSaRegs = (NT + 31) / 32;
-    float sa_next[kSaRegs], sw_next[4], bias_next[4];
+    const bool tl_warp = warp == 2 && lane == 0;
+    constexpr int kMine = (T::kChunks + kPairSub - 1) / kPairSub;     // chunks per warp and tile, at most
+    float sa_next[kMine], sw_next[4], bias_next[4];
     auto prefetch = [&](int t) {
       const int pch = (t % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane_ch;
       const int ptok0 = (t / tiles_ch2) * NT;
 #pragma unroll
-      for (int i = 0; i < kSaRegs; ++i) {
-        const int tok = ptok0 + lane + 32 * i;
-        sa_next[i] = (lane + 32 * i < NT && tok < args.m) ? __ldg(args.sa + tok) : 1.f;
+      for (int i = 0; i < kMine; ++i) {
+        const int in_tile = (half + kPairSub * i) * 32 + lane;
+        sa_next[i] = (in_tile < NT && ptok0 + in_tile < args.m) ? __ldg(args.sa + ptok0 + in_tile) : 1.f;
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {               // channels lane_ch + 8 i of the warp's 32
@@ -362,40 +494,51 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     };
     ptx::grid_dep_wait();             // sa is written by the kernel launched just before this one
     if (tile_first < num_tiles) prefetch(tile_first);
-    for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it) {
+    for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it, ++tl) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
       const int ch_w = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32;
       const int tok0 = (tile / tiles_ch2) * NT;
-      float sw[4], bias[4];
-      __syncwarp();
+      float sa_mine[kMine], sw[4], bias[4];
 #pragma unroll
-      for (int i = 0; i < kSaRegs; ++i)
-        if (lane + 32 * i < NT) sa_s[lane + 32 * i] = sa_next[i];
+      for (int i = 0; i < kMine; ++i) sa_mine[i] = sa_next[i];
 #pragma unroll
       for (int i = 0; i < 4; ++i) { sw[i] = sw_next[i]; bias[i] = bias_next[i]; }
-      __syncwarp();
       if (tile + tile_step < num_tiles) prefetch(tile + tile_step);
       int chunks = (args.m - tok0 + 31) / 32;
-      chunks = chunks < NT / 32 ? chunks : NT / 32;
-      if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u)) { ok = false; break; }
+      chunks = chunks < T::kChunks ? chunks : T::kChunks;
+      if (tl_warp) SS_TL(2, tl, 0);
+      if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u, args.wait_ns)) { ok = false; break; }
+      if (tl_warp) SS_TL(2, tl, 1);
       ptx::tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * NT;
       auto release = [&]() {
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_rank0(&bar_acc_empty[buf]);
+        if (tl_warp) SS_TL(2, tl, 2);
       };
+      if (args.debug & 2) {          // diagnostics: main loop alone, the accumulator is handed straight back
+        release();
+        continue;
+      }
       auto load = [&](uint32_t (&f)[32], int c) {
         ptx::tc_ld_16x256b_x4(t_addr + c * 32, f);                       // channels 0..15 of the quadrant
         ptx::tc_ld_16x256b_x4(t_addr + (16u << 16) + c * 32, f + 16);    // channels 16..31
       };
-      auto emit = [&](const uint32_t (&f)[32], int c) {
+      auto emit = [&](const uint32_t (&f)[32], int c, float sa_lane) {
         uint8_t* stage = smem + off_store + ((warp - 2) * kStoreBufs + (store_it % kStoreBufs)) * T::kStoreTile;
+        // scales of this thread's eight tokens (8 g + tpair, + 1), from the lanes that hold them
+        float2 sa_tok[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          sa_tok[g].x = __shfl_sync(0xffffffffu, sa_lane, 8 * g + tpair);
+          sa_tok[g].y = __shfl_sync(0xffffffffu, sa_lane, 8 * g + tpair + 1);
+        }
         if (lane == 0) {
+          // the staging tile about to be rewritten: its last store must have finished reading it
           if constexpr (kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
         }
         __syncwarp();
-        const float2* sa_c = reinterpret_cast<const float2*>(sa_s + c * 32 + tpair);
         // gated accumulation: the 32 tokens of a chunk belong to one batch (rows_per_batch % 32 == 0)
         float gate[4] = {1.f, 1.f, 1.f, 1.f};
         if constexpr (GATED) {
@@ -419,7 +562,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
             for (int gi = 0; gi < 2; ++gi) {
               const int g = 2 * gp + gi;
-              const float2 s = sa_c[4 * g];                                  // tokens 8 g + tpair, + 1
+              const float2 s = sa_tok[g];                                    // tokens 8 g + tpair, + 1
               const uint32_t* r = f + 16 * h + 4 * g;
 #pragma unroll
               for (int ab = 0; ab < 2; ++ab) {
@@ -445,14 +588,17 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) {
           // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
           // beyond the last channel is not issued at all
+          // the half chunk that ends a 240-token tile goes out through a 16-token box: the other 16
+          // staged rows hold columns of the neighbouring accumulator and belong to the next tile
+          const CUtensorMap* dst = (T::kHalfTail && c == T::kChunks - 1) ? &map_out_tail : &map_out;
           if (ch_w < args.n) {
             if constexpr (GATED) {
-              ptx::tma_reduce_add_2d(&map_out, stage, ch_w, tok0 + c * 32);
+              ptx::tma_reduce_add_2d(dst, stage, ch_w, tok0 + c * 32);
             } else if constexpr (MODE == kOutBf16TmaPeers) {
               // the same staged tile goes to this GPU's and every peer's gathered output
               for (int g = 0; g < args.peer_count; ++g) ptx::tma_store_2d(&peers.m[g], stage, ch_w, tok0 + c * 32);
             } else {
-              ptx::tma_store_2d(&map_out, stage, ch_w, tok0 + c * 32);
+              ptx::tma_store_2d(dst, stage, ch_w, tok0 + c * 32);
             }
           }
           ptx::bulk_commit();
@@ -463,21 +609,19 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       if (mine == 0) {
         release();
       } else {
-        uint32_t f0[32], f1[32];
-        load(f0, half);
-#pragma unroll 1
-        for (int i = 0; i < mine; i += 2) {
-          const int c = half + kPairSub * i;
-          ptx::tc_wait_ld();
-          if (i + 1 < mine) load(f1, c + kPairSub); else release();
-          emit(f0, c);
-          if (i + 1 < mine) {
+        uint32_t f[2][32];
+        load(f[0], half);
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) {
+          if (i < mine) {
+            const int c = half + kPairSub * i;
             ptx::tc_wait_ld();
-            if (i + 2 < mine) load(f0, c + 2 * kPairSub); else release();
-            emit(f1, c + kPairSub);
+            if (i + 1 < mine) load(f[(i + 1) & 1], c + kPairSub); else release();
+            emit(f[i & 1], c, sa_mine[i]);
           }
         }
       }
+      if (tl_warp) SS_TL(2, tl, 3);
     }
     if (lane == 0) ptx::bulk_wait_all();
     __syncwarp();
@@ -487,20 +631,19 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // (unaligned output, addend, INT32 dump): lane = channel, 32 token columns per tcgen05.ld
     const int quad = warp & 3;                    // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;             // which of the quadrant's warps: chunks half, half+kPairSub, ...
-    float* sa_s = reinterpret_cast<float*>(smem + off_sa) + (warp - 2) * NT;
     uint32_t acc_it = 0;
     bool ok = true;
-    // Scales of a tile are fetched one tile ahead into registers (the loads fly while the
-    // previous tile is processed) and parked in shared memory when the tile starts.
-    constexpr int kSaRegs = (NT + 31) / 32;
-    float sa_next[kSaRegs], sw_next = 1.f, bias_next = 0.f;
+    // Scales of a tile are fetched one tile ahead into registers (the loads fly while the previous
+    // tile is processed): lane l holds the scale of token l of each of the warp's chunks.
+    constexpr int kMine = (T::kChunks + kPairSub - 1) / kPairSub;
+    float sa_next[kMine], sw_next = 1.f, bias_next = 0.f;
     auto prefetch = [&](int t) {
       const int pch = (t % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
       const int ptok0 = (t / tiles_ch2) * NT;
 #pragma unroll
-      for (int i = 0; i < kSaRegs; ++i) {
-        const int tok = ptok0 + lane + 32 * i;
-        sa_next[i] = (lane + 32 * i < NT && tok < args.m) ? __ldg(args.sa + tok) : 1.f;
+      for (int i = 0; i < kMine; ++i) {
+        const int in_tile = (half + kPairSub * i) * 32 + lane;
+        sa_next[i] = (in_tile < NT && ptok0 + in_tile < args.m) ? __ldg(args.sa + ptok0 + in_tile) : 1.f;
       }
       sw_next = 1.f;
       bias_next = 0.f;
@@ -518,20 +661,19 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const int ch = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
       const int tok0 = (tile / tiles_ch2) * NT;
       const bool ch_ok = ch < args.n;
-      float sw = 1.f, bias = 0.f;
-      if constexpr (!INT32_OUT) {
-        __syncwarp();
+      float sa_mine[kMine], sw = 1.f, bias = 0.f;
 #pragma unroll
-        for (int i = 0; i < kSaRegs; ++i)
-          if (lane + 32 * i < NT) sa_s[lane + 32 * i] = sa_next[i];
+      for (int i = 0; i < kMine; ++i) sa_mine[i] = 1.f;
+      if constexpr (!INT32_OUT) {
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) sa_mine[i] = sa_next[i];
         sw = sw_next;
         bias = bias_next;
-        __syncwarp();
         if (tile + tile_step < num_tiles) prefetch(tile + tile_step);
       }
       int chunks = (args.m - tok0 + 31) / 32;
-      chunks = chunks < NT / 32 ? chunks : NT / 32;
-      if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u)) { ok = false; break; }
+      chunks = chunks < T::kChunks ? chunks : T::kChunks;
+      if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u, args.wait_ns)) { ok = false; break; }
       ptx::tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * NT;
       auto release = [&]() {
@@ -539,25 +681,24 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_rank0(&bar_acc_empty[buf]);
       };
-      uint32_t r0[32], r1[32];
-      auto emit = [&](const uint32_t (&r)[32], int c) {
-        store_chunk<INT32_OUT, HAS_ADDEND>(r, args, sa_s + c * 32, tok0 + c * 32, ch, ch_ok, sw, bias);
-      };
+      if (args.debug & 2) {
+        release();
+        continue;
+      }
+      const int tok_end = tok0 + NT < args.m ? tok0 + NT : args.m;
       const int mine = chunks > half ? (chunks - half + kPairSub - 1) / kPairSub : 0;
       if (mine == 0) {
         release();
       } else {
-        ptx::tc_ld_32x32b_x32(t_addr + half * 32, r0);
-#pragma unroll 1
-        for (int i = 0; i < mine; i += 2) {
-          const int c = half + kPairSub * i;
-          ptx::tc_wait_ld();
-          if (i + 1 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + kPairSub) * 32, r1); else release();
-          emit(r0, c);
-          if (i + 1 < mine) {
+        uint32_t r[2][32];
+        ptx::tc_ld_32x32b_x32(t_addr + half * 32, r[0]);
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) {
+          if (i < mine) {
+            const int c = half + kPairSub * i;
             ptx::tc_wait_ld();
-            if (i + 2 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + 2 * kPairSub) * 32, r0); else release();
-            emit(r1, c + kPairSub);
+            if (i + 1 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + kPairSub) * 32, r[(i + 1) & 1]); else release();
+            store_chunk<INT32_OUT, HAS_ADDEND>(r[i & 1], args, sa_mine[i], tok0 + c * 32, tok_end, ch, ch_ok, sw, bias);
           }
         }
       }

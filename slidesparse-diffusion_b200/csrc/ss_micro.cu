@@ -101,6 +101,97 @@ int run_rate(int iters, int with_cp, double* cycles_per_mma) {
 }  // namespace
 }  // namespace ss
 
+namespace ss {
+namespace {
+
+// One warp waits, with the given limit, on an mbarrier that nothing ever arrives on.  The wait
+// must run out, the kernel must record that in the device status word and return normally.
+__global__ void wait_limit_kernel(unsigned long long limit_ns, uint32_t* status, unsigned long long* elapsed_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    ptx::fence_barrier_init();
+    const uint64_t t0 = ptx::globaltimer_ns();
+    const bool arrived = ptx::mbar_wait(&bar, 0, limit_ns);
+    elapsed_ns[0] = ptx::globaltimer_ns() - t0;
+    if (!arrived) atomicOr(status, kStatusProbeTimeout);
+  }
+}
+
+}  // namespace
+}  // namespace ss
+
+extern "C" int ss_micro_wait_limit(int64_t limit_ns, int64_t* elapsed_ns) {
+  using namespace ss;
+  SS_REQUIRE(elapsed_ns, SS_E_ARG, "wait limit probe: result pointer required");
+  SS_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ll, SS_E_ARG,
+             "wait limit probe: limit must be between 1 ns and 100 ms (got %lld)", (long long)limit_ns);
+  uint32_t* status = device_status_ptr();
+  SS_REQUIRE(status, SS_E_CUDA, "device status word unavailable");
+  unsigned long long* d_elapsed = nullptr;
+  SS_CUDA(cudaMalloc(&d_elapsed, sizeof(unsigned long long)));
+  wait_limit_kernel<<<1, 32>>>(static_cast<unsigned long long>(limit_ns), status, d_elapsed);
+  unsigned long long host = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(&host, d_elapsed, sizeof(host), cudaMemcpyDeviceToHost);
+  cudaFree(d_elapsed);
+  SS_REQUIRE(e == cudaSuccess, SS_E_CUDA, "wait limit probe: %s", cudaGetErrorString(e));
+  *elapsed_ns = static_cast<int64_t>(host);
+  return SS_OK;
+}
+
+extern "C" int ss_micro_pair_rate(int64_t m, int64_t n, int64_t pk, int token_tile, int flags,
+                                  double* cycles_per_stage, int64_t* stages) {
+  using namespace ss;
+  SS_REQUIRE(cycles_per_stage && stages, SS_E_ARG, "pair rate: result pointers required");
+  SS_REQUIRE(m > 0 && n > 0 && pk > 0 && pk % 128 == 0 && m <= 65536 && n <= 65536 && pk <= 65536, SS_E_ARG,
+             "pair rate: sizes must be positive, pk a multiple of 128, each at most 65536");
+  SS_REQUIRE((flags & ~3) == 0, SS_E_ARG, "pair rate: flags are bit 0 (no MMAs) and bit 1 (no epilogue)");
+  const int64_t pm = ceil_to(m, 32), pn = ceil_to(n, 32);
+  const size_t q_bytes = static_cast<size_t>(pm) * pk, a_bytes = static_cast<size_t>(pn) * pk / 2;
+  const size_t e_bytes = static_cast<size_t>(pn) * pk / 8, o_bytes = static_cast<size_t>(m) * pn * 2;
+  unsigned char* base = nullptr;
+  const size_t v_bytes = static_cast<size_t>(pm + 2 * pn) * sizeof(float);
+  auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+  const size_t total = up(q_bytes) + up(a_bytes) + up(e_bytes) + up(o_bytes) + up(v_bytes) + 256;
+  SS_CUDA(cudaMalloc(&base, total));
+  unsigned char* q = base;
+  unsigned char* packed = q + up(q_bytes);
+  unsigned char* meta = packed + up(a_bytes);
+  unsigned char* out = meta + up(e_bytes);
+  float* vec = reinterpret_cast<float*>(out + up(o_bytes));
+  unsigned long long* probe = reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(vec) + up(v_bytes));
+  int rc = SS_OK;
+  // any bytes are valid operands; 0x44 nibbles are valid index pairs for the metadata
+  if (cudaMemset(q, 1, q_bytes) != cudaSuccess || cudaMemset(packed, 1, a_bytes) != cudaSuccess ||
+      cudaMemset(meta, 0x44, e_bytes) != cudaSuccess || cudaMemset(vec, 0, v_bytes) != cudaSuccess ||
+      cudaMemset(probe, 0, 16) != cudaSuccess)
+    rc = SS_E_CUDA;
+  Options& opt = options();
+  const int saved_tile = opt.token_tile, saved_resident = opt.resident;
+  opt.token_tile = token_tile;
+  GemmArgs a{reinterpret_cast<const int8_t*>(q), reinterpret_cast<const int8_t*>(packed),
+             reinterpret_cast<const int32_t*>(meta), vec, vec + pm, vec + pm + pn, nullptr, 0, out, pn,
+             m, n, pm, pn, pk, false};
+  a.debug = flags;
+  a.probe = probe;
+  for (int rep = 0; rep < 3 && rc == SS_OK; ++rep) {          // the first launches warm up
+    rc = launch_gemm(a, nullptr);
+    if (rc == SS_OK && cudaDeviceSynchronize() != cudaSuccess) rc = SS_E_CUDA;
+  }
+  opt.token_tile = saved_tile;
+  opt.resident = saved_resident;
+  unsigned long long host[2] = {0, 0};
+  if (rc == SS_OK && cudaMemcpy(host, probe, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess) rc = SS_E_CUDA;
+  if (rc == SS_E_CUDA) set_error("pair rate micro-benchmark: %s", cudaGetErrorString(cudaGetLastError()));
+  cudaFree(base);
+  if (rc != SS_OK) return rc;
+  SS_REQUIRE(host[1] > 0, SS_E_CUDA, "pair rate micro-benchmark: the kernel reported no stages");
+  *cycles_per_stage = static_cast<double>(host[0]) / static_cast<double>(host[1]);
+  *stages = static_cast<int64_t>(host[1]);
+  return SS_OK;
+}
+
 extern "C" int ss_micro_mma_rate(int token_tile, int sparse, int with_metadata_copy, int iterations,
                                  double* cycles_per_mma) {
   using namespace ss;

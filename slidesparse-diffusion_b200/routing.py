@@ -19,13 +19,15 @@ class ProjectionState:
         self.active = 0
         self.protected = int(protected_prefix)
         if self.protected and len(self.members) != 1:
-            raise ValueError("one original mixed output member required")
+            raise ValueError("a protected prefix belongs to a single output projection, not to fused members")
         self.widths = tuple(m.out_features for m in members)
         self.fuse = False      # run prologues inside the sparse operator's front-end kernel
 
     def select(self, mode):
-        if type(mode) is not int or mode not in (0, 4, 6, 8) or (mode and mode not in self.ops):
-            raise ValueError("missing frozen packed execution mode")
+        if type(mode) is not int or mode not in (0, 4, 6, 8):
+            raise ValueError(f"mode is 0 (dense) or a group size 4 / 6 / 8, not {mode!r}")
+        if mode != 0 and mode not in self.ops:
+            raise ValueError(f"no packed operator was prepared for mode {mode}")
         self.active = mode
 
     def _sparse(self, x, prologue):
@@ -46,7 +48,7 @@ class ProjectionState:
                 x = prologue.torch_reference(x)
             return tuple(module(x) for module in self.members)
         if self.protected:
-            raise ValueError("protected mixed output is not a shared member projection")
+            raise ValueError("a projection with a protected prefix has one output: use output()")
         return self._sparse(x, prologue).split(self.widths, dim=-1)
 
     def output(self, x, prologue=None, gated_residual=None):

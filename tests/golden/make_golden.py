@@ -94,7 +94,8 @@ def structured_weight(rng, n, k, l, density=0.9):
 
 def main():
     parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE", "/root/reference"))
+    parser.add_argument("--reference", default=os.environ.get("SS_REFERENCE"), required=not os.environ.get("SS_REFERENCE"),
+                        help="root of the SlideSparse-Diffusion source tree (or set SS_REFERENCE)")
     args = parser.parse_args()
     ref = Path(args.reference)
     packing = load_file("ref_packing", ref / "sdacc/w8a8_slidesparse/packing.py")

@@ -62,3 +62,39 @@ def prepare_case(oracle, m, k, n, mode, seed=0, with_bias=True):
     expect.update(x=x, qweight=qweight, scales=scales, bias=bias, pk=pk,
                   meta_b200=oracle.meta_to_b200(expect["raw"], pk))
     return expect
+
+
+def verify_accumulators(oracle, acc_cpu, q_ref, qweight, mode, m, n, rows=48, cols=160, seed=7):
+    """Full-size check of INT32 accumulators [m, n] without redoing the contraction on the CPU:
+    row and column checksums in int64 (every output element enters one of each) and an exact
+    comparison on a random sample of rows x columns."""
+    lifted = torch.from_numpy(oracle.slide_weight(qweight, mode)).to(torch.int64)          # [n, valid]
+    valid = lifted.shape[1]
+    q64 = torch.from_numpy(q_ref[:m, :valid]).to(torch.int64)
+    assert torch.equal(acc_cpu.sum(dim=1, dtype=torch.int64), q64 @ lifted.sum(dim=0))
+    assert torch.equal(acc_cpu.sum(dim=0, dtype=torch.int64), lifted @ q64.sum(dim=0))
+    gen = torch.Generator().manual_seed(seed)
+    r = torch.randperm(m, generator=gen)[:rows]
+    c = torch.randperm(n, generator=gen)[:cols]
+    assert torch.equal(acc_cpu[r][:, c].to(torch.int64), q64[r] @ lifted[c].T)
+
+
+class option:
+    """Context manager: one tuning switch of the native library set for the duration of a block."""
+
+    def __init__(self, backend, name, value):
+        self.backend, self.name, self.value = backend, name, value
+
+    def __enter__(self):
+        self.previous = self.backend.set_option(self.name, self.value)
+        return self
+
+    def __exit__(self, *exc):
+        self.backend.set_option(self.name, self.previous)
+
+
+def expected_bits(oracle, oracle_c, x, qweight, scales, bias, mode, addend_bits=None):
+    """BF16 bit patterns of the complete projection: the oracle's quantise / slide / contraction with
+    the C oracle's epilogue (a true fmaf, which settles the double-rounding corner cases)."""
+    ref = oracle.projection(x, qweight, scales, bias, mode)
+    return oracle_c.epilogue(ref["acc"], ref["sa"], scales, bias, addend_bits)

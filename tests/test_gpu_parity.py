@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from gpu_util import bits, c_gemm_int32, c_gemm_run, c_quantize_lift, prepare_case, ptr, stream, check
+from gpu_util import bits, c_gemm_int32, c_gemm_run, c_quantize_lift, option, prepare_case, ptr, stream, check
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -67,31 +67,51 @@ def test_gemm_int32_accumulators_bit_exact(backend, oracle, mode, m, k, n):
     assert np.array_equal(acc.cpu().numpy(), case["acc"])
 
 
-@pytest.mark.parametrize("pair,tile", [("1", "128"), ("1", "192"), ("1", "224"), ("1", "256"),
-                                       ("0", "64"), ("0", "128"), ("0", "192"), ("0", "256")])
-def test_every_kernel_variant_is_exact(backend, oracle, oracle_c, monkeypatch, pair, tile):
-    """CTA-pair kernel (default) and single-CTA kernel, every token tile, ragged edges in M, N, K."""
-    monkeypatch.setenv("SS_PAIR", pair)
-    monkeypatch.setenv("SS_TOKEN_TILE", tile)
-    case = prepare_case(oracle, 700, 640, 300, 6, seed=int(tile))
-    out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
-                     dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), 700, 300)
-    assert np.array_equal(bits(out), oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"]))
-    q, packed, meta = dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32)
-    acc = c_gemm_int32(backend, q, packed, meta, 700, 300)
+@pytest.mark.parametrize("tile", [128, 192, 224, 240, 256])
+@pytest.mark.parametrize("store", [1, 0])
+def test_every_kernel_variant_is_exact(backend, oracle, oracle_c, tile, store):
+    """Every token tile of the kernel (240 ends in a half chunk of 16 tokens), with the TMA-store
+    and the direct-store epilogue, ragged edges in M, N and K; BF16 output and INT32 dump."""
+    case = prepare_case(oracle, 700, 640, 300, 6, seed=tile)
+    with option(backend, "token_tile", tile), option(backend, "store", store):
+        wide = torch.full((700, 304), float("nan"), dtype=torch.bfloat16, device=DEV)   # 16-byte row pitch
+        lib = backend.library()
+        q, packed, meta = dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32)
+        sa, sw, bias = dev(case["sa"]), dev(case["scales"]), dev(case["bias"])
+        check(backend, lib.ss_gemm_run(ptr(q), ptr(packed), ptr(meta), ptr(sa), ptr(sw), ptr(bias), None, 0, ptr(wide), 304,
+                                       700, 300, q.shape[0], packed.shape[0], q.shape[1], stream()))
+        out = c_gemm_run(backend, q, packed, meta, sa, sw, bias, 700, 300)              # row pitch 300: direct stores
+        acc = c_gemm_int32(backend, q, packed, meta, 700, 300)
+    expect = oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"])
+    assert np.array_equal(bits(wide[:, :300]), expect)
+    assert torch.isnan(wide[:, 300:].float()).all()                # nothing written beyond the last channel
+    assert np.array_equal(bits(out), expect)
     assert np.array_equal(acc.cpu().numpy(), case["acc"])
     assert backend.device_status() == 0
 
 
 @pytest.mark.parametrize("mode,m,k,n", [(6, 1800, 256, 9216), (8, 3700, 384, 4500), (4, 4096, 1152, 4608), (4, 7300, 1280, 2304)])
-@pytest.mark.parametrize("resident", ["0", "1"])
-def test_weights_resident_form_is_exact(backend, oracle, oracle_c, monkeypatch, mode, m, k, n, resident):
-    """Shapes on which the weights-resident form of the pair kernel applies (short K, at least two
+@pytest.mark.parametrize("resident", [0, 1])
+def test_weights_resident_form_is_exact(backend, oracle, oracle_c, mode, m, k, n, resident):
+    """Shapes on which the weights-resident form of the kernel applies (short K, at least four
     token tiles per cluster), with it switched off and on: same bits either way, ragged M and N."""
-    monkeypatch.setenv("SS_RESIDENT", resident)
     case = prepare_case(oracle, m, k, n, mode, seed=m + n)
-    out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
-                     dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), m, n)
+    with option(backend, "resident", resident):
+        out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
+                         dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), m, n)
+    assert np.array_equal(bits(out), oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"]))
+    assert backend.device_status() == 0
+
+
+@pytest.mark.parametrize("tile", [224, 240, 256])
+def test_large_token_tiles_full_height(backend, oracle, oracle_c, tile):
+    """Several complete token tiles per cluster (so both accumulators and the half chunk of the
+    240-token tile are used repeatedly), aligned output."""
+    m, k, n, mode = 2 * 240 * 7 + 17, 512, 4096, 8
+    case = prepare_case(oracle, m, k, n, mode, seed=tile + 1)
+    with option(backend, "token_tile", tile), option(backend, "resident", 0):
+        out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
+                         dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), m, n)
     assert np.array_equal(bits(out), oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"]))
     assert backend.device_status() == 0
 

@@ -53,12 +53,13 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tensor_parallel_variants_match_the_oracle():
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tensor_parallel_variants_match_the_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
-    world = 2
     manager = mp.Manager()
     results = manager.dict()
     port = 29600 + os.getpid() % 1000
     mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
-    assert dict(results) == {0: "ok", 1: "ok"}
+    assert dict(results) == {rank: "ok" for rank in range(world)}
