@@ -1,10 +1,10 @@
 """Benchmark of the sparse W8A8 projection path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--only sweep]
 
-Workload ("flux_sweep"): the sliding-sparse projection sweep of the FLUX shapes -- modes 4:6 and
-6:8; (K,N) in {(3072,9216) fused QKV, (3072,12288) MLP fc1, (12288,3072) MLP fc2};
-M in {256, 1024, 1536, 4096, 16384}: 30 complete projections (front-end + GEMM) per step.
+Workload of the headline number ("flux_sweep"): the sliding-sparse projection sweep of the FLUX
+shapes -- modes 4:6 and 6:8; (K,N) in {(3072,9216) fused QKV, (3072,12288) MLP fc1, (12288,3072)
+MLP fc2}; M in {256, 1024, 1536, 4096, 16384}: 30 complete projections (front-end + GEMM) per step.
 Inputs are seeded synthetic tensors (BF16 N(0,1) activations with 1% outlier channels x20;
 N(0,0.02) weights magnitude-pruned per mode, per-channel INT8).
 
@@ -17,18 +17,25 @@ Printed JSON line (rank 0):
   roofline the GEMM kernel alone (CUDA events around GEMM-only launches), against the 2:4-sparse
            INT8 tensor peak derived from the measured dense BF16 peak (x4)
   cpu_baseline  the oracle port of the reference path timed on the host cores (bounded sample)
+  configs  the other benchmark configurations, measured in the same run (skipped with --only sweep):
+           the single 2:4 projection (4096 x 1152 -> 4608) against its binding (HBM) roof; one
+           denoise step of DiT-XL/2 512, PixArt-Sigma 1024 and the SD3.5-Large-style MMDiT with the
+           routed projections dense BF16 (eager, under torch.compile, before and after) and sparse
+           (neighbours left to PyTorch / fused into the kernels); the host cost of an eager forward.
+           With N > 1: the data-parallel denoising of 64 images split over the ranks, the sweep split
+           by output-channel columns over the ranks (strong scaling) and the N-split tensor-parallel
+           projection in its NCCL and its fused-store form next to the unsharded time on one GPU.
 
 `--impl reference` times the reference's CPU implementation of the path (its quantise / slide /
 pack restated in oracle/, with an int32 torch matmul) on a bounded sample of the same workload.
 With N > 1 (torchrun) every rank runs the sweep on its own weight shard (independent output
 channel shards, no collective); value = all ranks' operations / max-over-ranks time.
 
-`--workload dit-xl-512 | pixart-sigma-1024 | sd35-large-512` instead times one full denoise step
-(model forward on the CFG pair + guidance + sampler update, one CUDA graph) of a random-init
-transformer of that shape, with the routed projections sparse and with the same projections dense
-BF16 (dense measured before and after the sparse run); data-parallel over images when N > 1.
-`--workload compress` times the weight preparation (`reconstruction.compress`) of three weight
-shapes against the oracle port of the reference's algorithm on the host cores.
+Other workloads, one JSON line each: `--workload shapes [--shape LABEL]` (per-shape table: complete
+projection, GEMM, front-end and the paired BF16 dense projection), `--workload micro` (tensor-pipe
+and main-loop rates measured in the kernels), `--workload compress` (weight preparation against the
+oracle port on the host cores), `--workload dit-xl-512 | pixart-sigma-1024 | sd35-large-512` (one
+denoise step in detail, data-parallel over images when N > 1).
 """
 import argparse
 import json
@@ -247,9 +254,72 @@ CONFIG_SHAPES = (
 )
 
 
+def graph_time_us(torch, device, fn, calls, steps, warmup):
+    """Microseconds per call of `fn` (which makes `calls` calls) replayed as one CUDA graph."""
+    s = torch.cuda.Stream(device)
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        fn()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    for _ in range(max(warmup, 3)):
+        g.replay()
+    torch.cuda.synchronize()
+    b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b.record()
+    for _ in range(steps):
+        g.replay()
+    e.record()
+    torch.cuda.synchronize()
+    return b.elapsed_time(e) * 1e3 / (steps * calls)
+
+
+def measure_shape(torch, sdk, oracle, device, label, mode, m, k, n, steps, warmup):
+    """One row of the per-shape table: complete projection, GEMM alone, front-end alone and the paired
+    BF16 dense projection, each as a CUDA-graph replay over enough independent operand copies to
+    exceed L2 (every call reads its weights and activations from HBM), with the roofs that bound it."""
+    pk = peaks()
+    _, pkk = sdk.lifted_k(k, mode)
+    per_call = n * pkk * 5 // 8 + m * k * 2 + m * n * 2
+    copies = max(2, min(24, -(-300_000_000 // per_call)))
+    qweight, scales = oracle.make_weight(n, k, mode, seed=n + k + mode)
+    base = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales),
+                                    0.1 * torch.randn(n), mode).to(device)
+    ops = [base] + [sdk.PackedLinear(base.packed.clone(), base.metadata.clone(), base.scales.clone(),
+                                     base.bias.clone(), k, n, mode) for _ in range(copies - 1)]
+    x0 = oracle.make_activation(m, k, seed=m + k).to(device)
+    xs = [x0.clone() for _ in range(copies)]
+    dense_w = [(0.02 * torch.randn(n, k, device=device)).to(torch.bfloat16) for _ in range(copies)]
+    dense_b = torch.zeros(n, device=device, dtype=torch.bfloat16)
+    quantised = [sdk.quantize_lift(x, mode) for x in xs]
+    timed = lambda fn: graph_time_us(torch, device, fn, copies, steps, warmup)
+    full_us = timed(lambda: [op(x) for op, x in zip(ops, xs)])
+    gemm_us = timed(lambda: [torch.ops.sdacc_dualscale_sm80.run(q, op.packed, op.metadata, sa, op.scales, op.bias,
+                                                               m, n, 5, None) for op, (q, sa) in zip(ops, quantised)])
+    front_us = timed(lambda: [torch.ops.sdacc_mild_projection_sm80.quantize(x, mode) for x in xs])
+    dense_us = timed(lambda: [torch.nn.functional.linear(x, w, dense_b) for x, w in zip(xs, dense_w)])
+    pm, pn = -(-m // 32) * 32, -(-n // 32) * 32
+    gemm_bytes = pn * pkk // 2 + pn * pkk // 8 + pm * pkk + 4 * pm + 8 * n + 2 * m * n
+    front_bytes = 2 * m * k + pm * (pkk + 4)
+    t_hbm_us = gemm_bytes / pk["hbm_gbs"] / 1e3
+    t_tensor_us = 2.0 * pm * pn * pkk / (4.0 * pk["bf16_tflops"]) / 1e6
+    return {"shape": label, "mode": f"{mode - 2}:{mode}", "m": m, "k": k, "n": n, "copies": copies,
+            "projection_us": full_us, "gemm_us": gemm_us, "frontend_us": front_us, "dense_bf16_us": dense_us,
+            "logical_tops": 2.0 * m * n * k / full_us / 1e6,
+            "gemm_executed_pct_of_9000": 100 * 2.0 * pm * pn * pkk / gemm_us / 1e6 / 9000.0,
+            "gemm_algorithmic_bytes": gemm_bytes, "gemm_hbm_floor_us": t_hbm_us, "gemm_tensor_floor_us": t_tensor_us,
+            "gemm_binding_roof": "hbm" if t_hbm_us >= t_tensor_us else "tensor",
+            "gemm_frac_of_binding_roof": max(t_hbm_us, t_tensor_us) / gemm_us,
+            "frontend_gbs": front_bytes / front_us / 1e3, "frontend_frac_of_hbm": front_bytes / front_us / 1e3 / pk["hbm_gbs"],
+            "speedup_vs_dense": dense_us / full_us}
+
+
 def run_shapes(args, local_rank):
-    """Per-shape table: complete projection, GEMM alone, front-end alone and the paired BF16 dense
-    projection, each as a CUDA-graph replay over enough independent operand copies to exceed L2."""
+    """Per-shape table over every routed projection shape of the benchmark configurations (or the one
+    whose label --shape names)."""
     import torch
     from __graft_entry__ import load_package, load_oracle
     sdk = load_package()
@@ -257,62 +327,16 @@ def run_shapes(args, local_rank):
     oracle, _ = load_oracle()
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    pk = peaks()
     rows = []
-
-    def timed(fn, calls):
-        s = torch.cuda.Stream(device)
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            fn()
-        torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            fn()
-        for _ in range(max(args.warmup, 3)):
-            g.replay()
-        torch.cuda.synchronize()
-        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        b.record()
-        for _ in range(args.steps):
-            g.replay()
-        e.record()
-        torch.cuda.synchronize()
-        return b.elapsed_time(e) * 1e3 / (args.steps * calls)
-
     for label, mode, m, k, n in CONFIG_SHAPES:
-        _, pkk = sdk.lifted_k(k, mode)
-        per_call = n * pkk * 5 // 8 + m * k * 2 + m * n * 2
-        copies = max(2, min(24, -(-300_000_000 // per_call)))
-        qweight, scales = oracle.make_weight(n, k, mode, seed=n + k + mode)
-        base = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales),
-                                        0.1 * torch.randn(n), mode).to(device)
-        ops = [base] + [sdk.PackedLinear(base.packed.clone(), base.metadata.clone(), base.scales.clone(),
-                                         base.bias.clone(), k, n, mode) for _ in range(copies - 1)]
-        x0 = oracle.make_activation(m, k, seed=m + k).to(device)
-        xs = [x0.clone() for _ in range(copies)]
-        dense_w = [(0.02 * torch.randn(n, k, device=device)).to(torch.bfloat16) for _ in range(copies)]
-        dense_b = torch.zeros(n, device=device, dtype=torch.bfloat16)
-        quantised = [sdk.quantize_lift(x, mode) for x in xs]
-        full_us = timed(lambda: [op(x) for op, x in zip(ops, xs)], copies)
-        gemm_us = timed(lambda: [torch.ops.sdacc_dualscale_sm80.run(q, op.packed, op.metadata, sa, op.scales, op.bias,
-                                                                   m, n, 5, None) for op, (q, sa) in zip(ops, quantised)], copies)
-        front_us = timed(lambda: [torch.ops.sdacc_mild_projection_sm80.quantize(x, mode) for x in xs], copies)
-        dense_us = timed(lambda: [torch.nn.functional.linear(x, w, dense_b) for x, w in zip(xs, dense_w)], copies)
-        pm, pn = -(-m // 32) * 32, -(-n // 32) * 32
-        rows.append({"shape": label, "mode": f"{mode - 2}:{mode}", "m": m, "k": k, "n": n, "copies": copies,
-                     "projection_us": full_us, "gemm_us": gemm_us, "frontend_us": front_us, "dense_bf16_us": dense_us,
-                     "logical_tops": 2.0 * m * n * k / full_us / 1e6,
-                     "gemm_executed_pct_of_9000": 100 * 2.0 * pm * pn * pkk / gemm_us / 1e6 / 9000.0,
-                     "frontend_gbs": (2 * m * k + pm * (pkk + 4)) / front_us / 1e3,
-                     "speedup_vs_dense": dense_us / full_us})
-        del ops, xs, dense_w, quantised, base
+        if args.shape and args.shape.lower() not in label.lower():
+            continue
+        rows.append(measure_shape(torch, sdk, oracle, device, label, mode, m, k, n, args.steps, args.warmup))
         torch.cuda.empty_cache()
     print(json.dumps({"metric": "projection_shape_table", "unit": "us", "n_gpus": 1, "steps": args.steps,
                       "warmup": max(args.warmup, 3), "data": "synthetic", "dtype": "int8",
                       "config": {"workload": "shapes", "l2": "operand copies rotate so each step exceeds L2"},
-                      "peaks": pk, "rows": rows}))
+                      "peaks": peaks(), "rows": rows}))
 
 
 def run_micro(local_rank):
@@ -336,8 +360,25 @@ def run_micro(local_rank):
                          "operand_bytes_per_cycle": operand_bytes / cycles})
     rows.append({"kind": "sparse i8 K=64 + metadata copy per 2 MMAs", "token_tile": 256,
                  "cycles_per_mma": backend.micro_mma_rate(256, True, True)})
+    # the real kernel (CTA pairs, TMA producer, metadata copies) with parts switched off: cycles per
+    # pipeline stage of 256 lifted columns (= four MMAs of the pair = 2 x token tile tensor cycles)
+    pair_rows = []
+    cases = (("one cluster alone, K'=16384", lambda nt: (nt, 256, 16384)),
+             ("all 74 clusters, 4096 x 9216, K'=4096", lambda nt: (4096, 9216, 4096)))
+    for what, problem in cases:
+        for nt in (128, 192, 224, 240, 256):
+            m, n, pk = problem(nt)
+            row = {"case": what, "token_tile": nt, "tensor_cycles_per_stage": 2 * nt}
+            for name, kw in (("kernel", {}), ("no_epilogue", dict(no_epilogue=True)),
+                             ("feed_only", dict(no_mma=True, no_epilogue=True))):
+                cycles, stages = backend.micro_pair_rate(m, n, pk, nt, **kw)
+                row[name + "_cycles_per_stage"] = cycles
+            row["stages_timed"] = stages
+            row["tensor_pipe_pct_main_loop_alone"] = 100.0 * 2 * nt / row["no_epilogue_cycles_per_stage"]
+            row["tensor_pipe_pct_kernel"] = 100.0 * 2 * nt / row["kernel_cycles_per_stage"]
+            pair_rows.append(row)
     print(json.dumps({"metric": "mma_cycles", "unit": "cycles", "n_gpus": 1, "data": "synthetic", "dtype": "int8",
-                      "config": {"workload": "micro"}, "rows": rows}))
+                      "config": {"workload": "micro"}, "rows": rows, "pair_main_loop": pair_rows}))
 
 
 def run_compress(args, local_rank):
@@ -393,20 +434,17 @@ def run_compress(args, local_rank):
                                                              "method": "joint"}, "rows": rows_out}))
 
 
-def run_denoise(args, rank, world, local_rank):
-    """Denoise-step latency: sparse routed projections against dense BF16 on the same model."""
-    import torch
-    import torch.distributed as dist
-    from __graft_entry__ import load_package
-    sdk = load_package()
-    sdk.load_native()
+def denoise_legs(torch, dist, name, device, rank, world, steps, warmup, images=1, compiled_blocks=4):
+    """One denoise step (model forward on the CFG batch + guidance + sampler update, one CUDA graph) of
+    a random-init transformer of configuration `name`, in every form the comparison needs:
+    routed projections dense BF16 (eager kernels; measured before and after the sparse legs), sparse
+    with the element-wise neighbours left to PyTorch, sparse with the neighbours fused into the
+    front-end / epilogue.  The reference's dense comparator is the model under torch.compile
+    (sdacc/diffusion_research/runtime.py:108): its gain over eager kernels is measured on an instance
+    of `compiled_blocks` blocks (compiling the full depth would take minutes) and applied to the
+    full-depth eager time.  Times are ms per step, max over ranks."""
     from slidesparse_diffusion_b200 import denoiser, backend
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    overrides = {} if args.blocks is None else {"blocks": args.blocks}
-    model = denoiser.build(args.workload, device=device, seed=rank, **overrides)
+    model = denoiser.build(name, device=device, seed=rank)
     spec = model.spec
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
@@ -416,86 +454,335 @@ def run_denoise(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(loop, steps, warmup):
-        """ms per denoise step over `steps` steps of the sampling loop (max over ranks)."""
+    def timed(loop, count):
         loop.run(seed=rank, steps=max(warmup, 3))
         barrier()
         begin.record()
-        loop.run(seed=rank, steps=steps)
+        loop.run(seed=rank, steps=count)
         end.record()
         barrier()
-        t = torch.tensor([begin.elapsed_time(end) / steps], device=device)
+        t = torch.tensor([begin.elapsed_time(end) / count], device=device)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    steps = min(args.steps, spec.steps)
-    if args.variant != "all":
-        # one leg alone (for a launch list of exactly that variant): dense, or sparse with fused neighbours
-        if args.variant == "fused":
-            model.select(model.pack())
-            model.fuse_neighbours(True)
-        else:
-            model.select(0)
-        only = timed(denoiser.DenoiseLoop(model, graph=True, images=args.images), steps, args.warmup)
-        if rank == 0:
-            print(json.dumps({"metric": "denoise_step_ms", "value": only, "unit": "ms", "n_gpus": world,
-                              "steps": steps, "higher_is_better": False, "data": "synthetic",
-                              "config": {"workload": args.workload, "variant": args.variant, "blocks": spec.blocks}}))
-        if world > 1:
-            dist.destroy_process_group()
-        return
+    count = min(steps, spec.steps)
     model.select(0)
-    dense_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
-    dense_before = timed(dense_loop, steps, args.warmup)
+    dense_loop = denoiser.DenoiseLoop(model, graph=True, images=images)
+    dense_before = timed(dense_loop, count)
     t0 = time.time()
     mode = model.pack()
     torch.cuda.synchronize()
     pack_s = time.time() - t0
     model.select(mode)
-    plain_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
-    sparse_plain_ms = timed(plain_loop, steps, args.warmup)      # neighbours as separate PyTorch kernels
-    model.fuse_neighbours(True)                                  # LayerNorm+modulate and GELU inside the front-end
-    sparse_loop = denoiser.DenoiseLoop(model, graph=True, images=args.images)
-    with ClockSampler(local_rank) as clocks:
-        sparse_ms = timed(sparse_loop, steps, args.warmup)
+    sparse_plain_ms = timed(denoiser.DenoiseLoop(model, graph=True, images=images), count)
+    model.fuse_neighbours(True)
+    sparse_loop = denoiser.DenoiseLoop(model, graph=True, images=images)
+    with ClockSampler(device.index) as clocks:
+        sparse_ms = timed(sparse_loop, count)
     if backend.device_status(device) != 0:
         raise SystemExit("bench: a kernel reported a bounded wait that ran out")
-    dense_after = timed(dense_loop, steps, args.warmup)
-
+    dense_after = timed(dense_loop, count)
     # end to end through the public loop: seeded host noise in, final latent back on the host
     barrier()
     begin.record()
-    latent = sparse_loop.run(seed=rank + 100, steps=steps).cpu()
+    latent = sparse_loop.run(seed=rank + 100, steps=count).cpu()
     end.record()
     barrier()
-    e2e_ms = begin.elapsed_time(end) / steps
-    projections = len(model.units)
+    e2e_ms = begin.elapsed_time(end) / count
+    projections, sparse_units = len(model.units), model.sparse_units(mode)
+    del dense_loop, sparse_loop
+    model.select(0)
+    dense_ms = min(dense_before, dense_after)
+
+    compiled = None
+    if compiled_blocks:
+        try:
+            small = denoiser.build(name, device=device, seed=rank, blocks=compiled_blocks)
+            small.select(0)
+            eager_small = timed(denoiser.DenoiseLoop(small, graph=True, images=images), count)
+            torch._dynamo.config.cache_size_limit = 512
+            loop = denoiser.DenoiseLoop(small, graph=True, images=images)
+            loop.model = torch.compile(small, fullgraph=True, dynamic=False)
+            t0 = time.time()
+            compiled_small = timed(loop, count)
+            ratio = compiled_small / eager_small
+            # the reference compiles its sparse model too (the operators are opaque to the compiler, the
+            # element-wise neighbours around them get fused by it): the same instance, sparse, compiled
+            small.select(small.pack())
+            sparse_eager_small = timed(denoiser.DenoiseLoop(small, graph=True, images=images), count)
+            loop = denoiser.DenoiseLoop(small, graph=True, images=images)
+            loop.model = torch.compile(small, fullgraph=True, dynamic=False)
+            sparse_compiled_small = timed(loop, count)
+            small.fuse_neighbours(True)
+            sparse_fused_small = timed(denoiser.DenoiseLoop(small, graph=True, images=images), count)
+            compiled = {"blocks": compiled_blocks, "eager_ms": eager_small, "compiled_ms": compiled_small,
+                        "compiled_over_eager": ratio, "compile_seconds": time.time() - t0,
+                        "full_depth_estimate_ms": dense_ms * ratio,
+                        "sparse_pytorch_neighbours_ms": sparse_eager_small, "sparse_compiled_ms": sparse_compiled_small,
+                        "sparse_fused_neighbours_ms": sparse_fused_small,
+                        "speedup_both_compiled": compiled_small / sparse_compiled_small,
+                        "what": f"torch.compile(fullgraph=True) of a {compiled_blocks}-block instance of the model, dense and "
+                                "sparse; the dense ratio is applied to the full-depth eager time"}
+            del small, loop
+        except Exception as e:        # noqa: BLE001 - the compiler stack may be unusable on a box
+            compiled = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+    del model
+    torch.cuda.empty_cache()
+    dense_compiled_ms = compiled.get("full_depth_estimate_ms") if compiled else None
+    return {
+        "workload": name, "mode": f"{mode - 2}:{mode}", "blocks": spec.blocks, "hidden": spec.hidden,
+        "image_tokens": spec.tokens, "text_tokens": spec.text_tokens, "cfg_batch": 2 * images, "sampler": spec.sampler,
+        "sampler_steps": spec.steps, "timed_steps": count, "routed_projections": projections,
+        "sparse_projections": sparse_units,
+        "dense_bf16_eager_ms": dense_ms, "dense_bf16_ms_before": dense_before, "dense_bf16_ms_after": dense_after,
+        "dense_bf16_compiled": compiled,
+        "sparse_pytorch_neighbours_ms": sparse_plain_ms, "sparse_fused_neighbours_ms": sparse_ms,
+        "speedup_like_for_like": dense_ms / sparse_plain_ms, "speedup_fused_vs_dense_eager": dense_ms / sparse_ms,
+        "speedup_fused_vs_dense_compiled": (dense_compiled_ms / sparse_ms) if dense_compiled_ms else None,
+        "images_per_s": world * images / (spec.steps * sparse_ms * 1e-3), "pack_seconds": pack_s,
+        "e2e_ms_per_step": e2e_ms, "e2e_bytes_per_step": latent.numel() * 4 // count,
+        "gpu_launches_per_step": 2 * sparse_units, "clocks": clocks.summary(),
+    }
+
+
+def run_denoise(args, rank, world, local_rank):
+    """Denoise-step latency of one configuration as its own JSON line."""
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    sdk = load_package()
+    sdk.load_native()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    legs = denoise_legs(torch, dist, args.workload, device, rank, world, args.steps, args.warmup, images=args.images)
     if rank == 0:
-        dense_ms = min(dense_before, dense_after)
         print(json.dumps({
-            "metric": "denoise_step_ms", "value": sparse_ms, "unit": "ms", "n_gpus": world, "steps": steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": sparse_ms, "higher_is_better": False, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": args.workload, "mode": f"{mode - 2}:{mode}", "blocks": spec.blocks,
-                       "hidden": spec.hidden, "image_tokens": spec.tokens, "text_tokens": spec.text_tokens,
-                       "cfg_batch": 2 * args.images, "sampler": spec.sampler, "sampler_steps": spec.steps,
-                       "routed_projections": projections, "sparse_projections": model.sparse_units(mode),
-                       "parallelism": f"data-parallel images x{world}",
+            "metric": "denoise_step_ms", "value": legs["sparse_fused_neighbours_ms"], "unit": "ms", "n_gpus": world,
+            "steps": legs["timed_steps"], "warmup": max(args.warmup, 3), "ms_per_step": legs["sparse_fused_neighbours_ms"],
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": args.workload, "parallelism": f"data-parallel images x{world}",
                        "l2": "weights per step exceed L2"},
-            "clocks": clocks.summary(),
-            "dense_bf16": {"ms_before": dense_before, "ms_after": dense_after, "speedup": dense_ms / sparse_ms,
-                           "what": "same model, routed projections as BF16 nn.Linear, neighbours as PyTorch kernels"},
-            "sparse_unfused_neighbours": {"ms": sparse_plain_ms, "speedup_vs_dense": dense_ms / sparse_plain_ms,
-                                          "what": "sparse projections with LayerNorm+modulate and GELU left to PyTorch"},
-            "images_per_s": world * args.images / (spec.steps * sparse_ms * 1e-3),
-            "pack_seconds": pack_s,
-            "e2e": {"value": e2e_ms, "unit": "ms", "h2d_bytes_per_step": latent.numel() * 4 // steps,
-                    "d2h_bytes_per_step": latent.numel() * 4 // steps},
-            "gpu_launches": 2 * model.sparse_units(mode) * steps,
+            "clocks": legs["clocks"], "legs": legs,
+            "e2e": {"value": legs["e2e_ms_per_step"], "unit": "ms", "h2d_bytes_per_step": legs["e2e_bytes_per_step"],
+                    "d2h_bytes_per_step": legs["e2e_bytes_per_step"]},
+            "gpu_launches": legs["gpu_launches_per_step"] * legs["timed_steps"],
         }))
     if world > 1:
         dist.destroy_process_group()
+
+
+def data_parallel_images(torch, dist, device, rank, world, total_images=64, per_forward=4, timed_steps=2, warmup=3):
+    """Configuration 5 as stated: a batch of 64 images denoised data-parallel, rank r taking images
+    r, r + world, ... (denoiser.images_for_rank), `per_forward` images (CFG batch 2 x that) per model
+    call, no exchange inside the loop.  Every rank really runs all of its batches, but only
+    `timed_steps` sampler steps of each (a full run is 25 steps per batch: minutes at one GPU); the
+    images/s figure scales the measured time per step to the sampler's step count."""
+    from slidesparse_diffusion_b200 import denoiser, backend
+    name = "sd35-large-512"
+    model = denoiser.build(name, device=device, seed=0)
+    spec = model.spec
+    mine = denoiser.images_for_rank(total_images, rank, world)
+    batches = [mine[i:i + per_forward] for i in range(0, len(mine), per_forward)]
+    out = {}
+    for leg in ("dense_bf16_eager", "sparse_fused_neighbours"):
+        if leg != "dense_bf16_eager":
+            model.select(model.pack())
+            model.fuse_neighbours(True)
+        else:
+            model.select(0)
+        loops = {}
+        for size in sorted({len(b) for b in batches}):
+            loops[size] = denoiser.DenoiseLoop(model, graph=True, images=size)
+            loops[size].run(seed=rank, steps=max(warmup, 3))
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        begin.record()
+        for b in batches:
+            loops[len(b)].run(seed=b[0], steps=timed_steps)
+        end.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([begin.elapsed_time(end)], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_timed = float(t.item())
+        full_ms = ms_timed * spec.steps / timed_steps
+        out[leg] = {"ms_for_timed_steps": ms_timed, "images_per_s": total_images / (full_ms * 1e-3),
+                    "ms_per_step_and_batch": ms_timed / (timed_steps * max(1, len(batches)))}
+        del loops
+    if backend.device_status(device) != 0:
+        raise SystemExit("bench: a kernel reported a bounded wait that ran out")
+    del model
+    torch.cuda.empty_cache()
+    out.update(workload=name, total_images=total_images, images_per_forward=per_forward, images_this_rank=len(mine),
+               batches_this_rank=len(batches), timed_sampler_steps_per_batch=timed_steps, sampler_steps=spec.steps,
+               parallelism=f"data-parallel over images x{world}, no collective inside the loop",
+               speedup_vs_dense_eager=out["sparse_fused_neighbours"]["images_per_s"] / out["dense_bf16_eager"]["images_per_s"])
+    return out
+
+
+def tensor_parallel_variant(torch, dist, sdk, oracle, device, rank, world, barrier):
+    """The N-split tensor-parallel projection at `world` GPUs: NCCL all-gather form (row-major result
+    and the collective's own shard-major result) and the form whose gather is done by the GEMM
+    epilogue's stores into every rank's buffer, each next to the unsharded projection on one GPU."""
+    from slidesparse_diffusion_b200 import sharding
+    rows = []
+    for m, k, n, mode in ((1536, 3072, 12288, 6), (16384, 12288, 3072, 6)):
+        qweight, scales = oracle.make_weight(n, k, mode, seed=77)
+        qw, sc = torch.from_numpy(qweight), torch.from_numpy(scales)
+        shard, _ = sharding.prepare_shard(qw, sc, None, mode, rank, world)
+        bounds = sharding.shard_columns(n, world)
+        shard = shard.to(device)
+        x = oracle.make_activation(m, k, seed=k).to(device)
+        row = {"shape_mkn": [m, k, n], "mode": f"{mode - 2}:{mode}", "gathered_output_mb": 2 * m * n / 1e6}
+
+        def timed(fn, label):
+            """ms per call, max over ranks; one CUDA graph of 5 calls if the form can be captured."""
+            for _ in range(3):
+                fn()
+            launch = "graph"
+            try:
+                side = torch.cuda.Stream(device)
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    fn()
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    for _ in range(5):
+                        fn()
+                run, per = graph.replay, 5
+                run()
+            except Exception:         # noqa: BLE001 - a form that cannot be captured is timed eagerly
+                torch.cuda.synchronize()
+                launch, run, per = "eager", fn, 1
+            flag = torch.tensor([1 if launch == "graph" else 0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0 and launch == "graph":
+                launch, run, per = "eager", fn, 1
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            begin.record()
+            for _ in range(4):
+                run()
+            end.record()
+            barrier()
+            t = torch.tensor([begin.elapsed_time(end) / (4 * per)], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            row[label + "_ms"] = float(t.item())
+            row[label + "_launch"] = launch
+
+        tp_op = sharding.TensorParallelProjection(shard, bounds)
+        timed(lambda: tp_op(x), "nccl_rows")
+        timed(lambda: tp_op(x, layout="shards"), "nccl_shards")
+        reference = tp_op(x)
+        # the fused form needs symmetric memory on every rank: agree on it before any rank enters it
+        fused_op, ok = None, 1
+        try:
+            fused_op = sharding.FusedTensorParallelProjection(shard, bounds)
+            fused_op(x)
+        except Exception as e:        # noqa: BLE001
+            ok, row["fused_store_error"] = 0, f"{type(e).__name__}: {str(e)[:160]}"
+        flag = torch.tensor([ok], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            timed(lambda: fused_op(x), "fused_store")
+            row["fused_store_equals_nccl"] = bool(torch.equal(fused_op(x), reference))
+        elif "fused_store_error" not in row:
+            row["fused_store_error"] = "symmetric memory unavailable on another rank"
+        if rank == 0:
+            # the same projection unsharded on this one GPU
+            whole = sdk.PackedLinear.prepare(qw, sc, None, mode).to(device)
+            row["single_gpu_unsharded_ms"] = graph_time_us(torch, device, lambda: whole(x), 1, 10, 3) / 1e3
+            row["single_gpu_equals_tp"] = bool(torch.equal(whole(x), reference))
+            best = min(v for key, v in row.items() if key.endswith("_ms") and key != "single_gpu_unsharded_ms")
+            row["best_tp_over_single_gpu"] = row["single_gpu_unsharded_ms"] / best
+            row["nvlink_bound_ms"] = (world - 1) / world * 2 * m * n / 770e9 * 1e3
+            del whole
+        rows.append(row)
+        del shard, tp_op, fused_op
+        torch.cuda.empty_cache()
+    return {"world": world, "rows": rows,
+            "what": "N-split column shards; nccl_rows = all-gather + one re-ordering copy to [M, N]; nccl_shards = the "
+                    "all-gather alone ([world, M, N/world]); fused_store = every tile stored by the GEMM epilogue into all "
+                    "ranks' symmetric [M, N] buffers (TMA stores over NVLink) between two symmetric-memory barriers; "
+                    "nvlink_bound_ms = bytes a rank must receive / 770 GB/s"}
+
+
+def strong_scaling_sweep(torch, dist, sdk, oracle, device, rank, world, dev_x, calls, step_ops, steps, warmup, barrier):
+    """The SAME 30-projection sweep with every projection's output channels split over the ranks
+    (rank r computes columns [start_r, end_r) of each): fixed total work, so the aggregate rate is the
+    strong-scaling figure next to the replica-per-rank `value`."""
+    from slidesparse_diffusion_b200 import sharding
+    ops = {}
+    for mode in MODES:
+        for (k, n) in SHAPES:
+            qweight, scales = oracle.make_weight(n, k, mode, seed=mode * 100 + n % 97)      # same weight on every rank
+            bias = (0.1 * torch.randn(n, generator=torch.Generator().manual_seed(n))).float()
+            shard, _ = sharding.prepare_shard(torch.from_numpy(qweight), torch.from_numpy(scales), bias, mode, rank, world)
+            ops[(mode, k, n)] = shard.to(device)
+
+    def step():
+        return [ops[(mode, k, n)](dev_x[(m, k)]) for (mode, k, n, m) in calls]
+
+    side = torch.cuda.Stream(device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outputs = step()
+    for _ in range(max(warmup, 3)):
+        graph.replay()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    begin.record()
+    for _ in range(steps):
+        graph.replay()
+    end.record()
+    barrier()
+    t = torch.tensor([begin.elapsed_time(end)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    del outputs, graph, ops
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms, "tops": step_ops / (ms * 1e-3) / 1e12, "scaling": "strong",
+            "channels_per_rank": {f"{n}": -(-n // 32 // world) * 32 for (_, n) in SHAPES},
+            "what": "one sweep split by output-channel columns over the ranks, no collective; rate = total operations of "
+                    "ONE sweep / max-over-ranks time"}
+
+
+def eager_forward_cost(torch, sdk, oracle, device):
+    """Host cost of an eager PackedLinear.forward (two kernel launches): microseconds per call when
+    the calls are issued back to back without a graph, for a projection whose kernels take less than
+    that (the host path is what is timed), next to the same calls replayed as a graph."""
+    m, k, n, mode = 256, 1152, 1152, 4
+    qweight, scales = oracle.make_weight(n, k, mode, seed=3)
+    op = sdk.PackedLinear.prepare(torch.from_numpy(qweight), torch.from_numpy(scales), None, mode).to(device)
+    x = oracle.make_activation(m, k, seed=4).to(device)
+    for _ in range(20):
+        op(x)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    begin.record()
+    for _ in range(400):
+        op(x)
+    end.record()
+    host_us = (time.perf_counter() - t0) * 1e6 / 400
+    torch.cuda.synchronize()
+    return {"shape_mkn": [m, k, n], "eager_us_per_forward": begin.elapsed_time(end) * 1e3 / 400,
+            "host_us_per_forward": host_us,
+            "graph_replay_us_per_forward": graph_time_us(torch, device, lambda: [op(x) for _ in range(20)], 20, 20, 3),
+            "what": "PackedLinear.forward issued eagerly: operator dispatch, ctypes call, cached tensor maps, two launches"}
 
 
 def main():
@@ -504,15 +791,14 @@ def main():
     parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="native", choices=("native", "reference"))
-    parser.add_argument("--tokens", type=str, default=None, help="comma-separated M values (debug)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--only", default="all", choices=("all", "sweep"),
+                        help="'sweep': the headline sweep alone, without the `configs` block of the other configurations")
     parser.add_argument("--workload", default="flux_sweep",
                         choices=("flux_sweep", "shapes", "micro", "compress", "dit-xl-512", "pixart-sigma-1024",
                                  "sd35-large-512"))
+    parser.add_argument("--shape", default=None, help="shapes workload: only the rows whose label contains this text")
     parser.add_argument("--images", type=int, default=1, help="images per forward in the denoise workloads")
-    parser.add_argument("--blocks", type=int, default=None, help="override the block count (debug)")
-    parser.add_argument("--variant", default="all", choices=("all", "dense", "fused"),
-                        help="denoise workloads: time one leg alone (debug / profiling)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -544,7 +830,7 @@ def main():
     sdk = load_package()
     sdk.load_native()
     oracle, oracle_c = load_oracle()
-    tokens = tuple(int(t) for t in args.tokens.split(",")) if args.tokens else TOKENS
+    tokens = TOKENS
 
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -636,25 +922,7 @@ def main():
             torch.ops.sdacc_mild_projection_sm80.quantize(dev_x[(m, k)], mode)
 
     def timed_graph(fn, repeats):
-        s = torch.cuda.Stream(device)
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            fn()
-        torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            fn()
-        for _ in range(3):
-            g.replay()
-        torch.cuda.synchronize()
-        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        b.record()
-        for _ in range(repeats):
-            g.replay()
-        e.record()
-        torch.cuda.synchronize()
-        return b.elapsed_time(e) / repeats
+        return graph_time_us(torch, device, fn, 1, repeats, 3) / 1e3
 
     gemm_ms = timed_graph(gemm_only, max(3, args.steps // 2))
     front_ms = timed_graph(frontend_only, max(3, args.steps // 2))
@@ -685,26 +953,26 @@ def main():
 
     # uploads, kernels and downloads run on three streams so that PCIe traffic in both directions
     # overlaps the projections of neighbouring calls (what a serving loop around the module does)
-    main, up, down = torch.cuda.current_stream(), torch.cuda.Stream(device), torch.cuda.Stream(device)
+    main_stream, up, down = torch.cuda.current_stream(), torch.cuda.Stream(device), torch.cuda.Stream(device)
 
     def e2e_step():
         staged, ready = {}, {}
-        up.wait_stream(main)
+        up.wait_stream(main_stream)
         for c in calls:
             mode, k, n, m = c
             if (m, k) not in staged:
                 with torch.cuda.stream(up):
                     staged[(m, k)] = host_x[(m, k)].to(device, non_blocking=True)
                     ready[(m, k)] = up.record_event()
-                staged[(m, k)].record_stream(main)
-            main.wait_event(ready[(m, k)])
+                staged[(m, k)].record_stream(main_stream)
+            main_stream.wait_event(ready[(m, k)])
             y = ops[(mode, k, n)](staged[(m, k)])
-            done = main.record_event()
+            done = main_stream.record_event()
             y.record_stream(down)
             with torch.cuda.stream(down):
                 down.wait_event(done)
                 host_out[c].copy_(y, non_blocking=True)
-        main.wait_stream(down)
+        main_stream.wait_stream(down)
 
     e2e_steps = max(3, args.steps // 4)
     for _ in range(2):
@@ -721,6 +989,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = world * step_ops * e2e_steps / (e2e_ms * 1e-3) / 1e12
+    del host_out
 
     # ---- CPU baseline (rank 0, single GPU runs only) ----------------------------------------------
     cpu = None
@@ -730,56 +999,36 @@ def main():
         cpu_sample(oracle, prepared, threads)
         total_ops, total_s = 0, 0.0
         while total_s < 10.0:
-            o, s = cpu_sample(oracle, prepared, threads)
+            o, sec = cpu_sample(oracle, prepared, threads)
             total_ops += o
-            total_s += s
+            total_s += sec
         cpu = {"value": total_ops / total_s / 1e12, "unit": "TOPS", "cores": threads, "kind": "port",
                "sample": f"6 projections (4:6+6:8 x 3 FLUX shapes) at M=1536 restricted to {SAMPLE_TOKENS} "
                          f"token rows, repeated for {total_s:.1f} s"}
 
-    tp = None
-    if world > 1:
-        from slidesparse_diffusion_b200 import sharding
-        tp_m, tp_k, tp_n, tp_mode = 1536, 3072, 12288, 6
-        qweight, scales = oracle.make_weight(tp_n, tp_k, tp_mode, seed=77)
-        shard, _ = sharding.prepare_shard(torch.from_numpy(qweight), torch.from_numpy(scales), None, tp_mode, rank, world)
-        tp_op = sharding.TensorParallelProjection(shard.to(device), sharding.shard_columns(tp_n, world))
-        tp_x = dev_x[(tp_m, tp_k)]
-        for _ in range(3):
-            tp_op(tp_x)
-        barrier()
-        begin.record()
-        for _ in range(10):
-            tp_op(tp_x)
-        end.record()
-        barrier()
-        t = torch.tensor([begin.elapsed_time(end) / 10], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        tp = {"shape_mkn": [tp_m, tp_k, tp_n], "mode": "4:6", "ms": float(t.item()),
-              "what": "N-split shards + NCCL all-gather of BF16 outputs, eager launches"}
-        # the same with the gather done by the GEMM epilogue's stores into every rank's buffer; this
-        # variant has been run on 2 GPUs only, so larger worlds take it only when asked to
-        try:
-            if world > 2 and os.environ.get("SS_BENCH_TP_FUSED") != "1":
-                raise RuntimeError("not run: validated on 2 GPUs; set SS_BENCH_TP_FUSED=1 to time it on more")
-            fused_op = sharding.FusedTensorParallelProjection(shard.to(device), sharding.shard_columns(tp_n, world))
-            for _ in range(3):
-                fused_op(tp_x)
-            barrier()
-            begin.record()
-            for _ in range(10):
-                fused_op(tp_x)
-            end.record()
-            barrier()
-            t = torch.tensor([begin.elapsed_time(end) / 10], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            same = bool(torch.equal(fused_op(tp_x), tp_op(tp_x)))
-            tp["fused_store_ms"] = float(t.item())
-            tp["fused_store_equals_nccl"] = same
-            tp["fused_what"] = ("every tile stored by the GEMM epilogue into all ranks' symmetric output buffers "
-                                "(TMA stores over NVLink), framed by two symmetric-memory barriers")
-        except Exception as e:        # noqa: BLE001 - symmetric memory may be unavailable on a box
-            tp["fused_store_error"] = f"{type(e).__name__}: {e}"
+    # ---- the other benchmark configurations --------------------------------------------------------
+    del outputs, graph, quantised
+    torch.cuda.empty_cache()
+    configs = None
+    if args.only == "all":
+        configs = {}
+        if world == 1:
+            label, cmode, cm, ck, cn = CONFIG_SHAPES[0]
+            configs["single_2to4_projection"] = measure_shape(torch, sdk, oracle, device, label, cmode, cm, ck, cn,
+                                                               args.steps, args.warmup)
+            configs["eager_forward"] = eager_forward_cost(torch, sdk, oracle, device)
+            del ops
+            torch.cuda.empty_cache()
+            configs["denoise_step"] = [denoise_legs(torch, dist, name, device, rank, world, min(args.steps, 10), args.warmup)
+                                       for name in ("dit-xl-512", "pixart-sigma-1024", "sd35-large-512")]
+        else:
+            del ops
+            torch.cuda.empty_cache()
+            configs["sweep_split_by_columns"] = strong_scaling_sweep(torch, dist, sdk, oracle, device, rank, world, dev_x,
+                                                                     calls, step_ops, args.steps, args.warmup, barrier)
+            configs["tp_variant"] = tensor_parallel_variant(torch, dist, sdk, oracle, device, rank, world, barrier)
+        configs["data_parallel_64_images"] = data_parallel_images(torch, dist, device, rank, world)
+
     if rank == 0:
         line = {
             "metric": "sparse_w8a8_linear_tops", "value": value, "unit": "TOPS", "n_gpus": world,
@@ -811,7 +1060,7 @@ def main():
             "dense_bf16": {"ms_per_step": dense_ms, "tflops": step_ops / (dense_ms * 1e-3) / 1e12,
                            "sparse_ms_per_step_this_rank": elapsed_ms / args.steps,
                            "what": "torch.nn.functional.linear (cuBLAS BF16) over the same 30 calls, graph replay"},
-            "tp_variant": tp,
+            "configs": configs,
         }
         print(json.dumps(line))
     if world > 1:

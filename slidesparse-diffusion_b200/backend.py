@@ -84,6 +84,35 @@ def build_native(output=None, arch=ARCH, force=False):
     return receipt
 
 
+BINDING_NAME = "SOURCE_BINDING.json"
+
+
+def source_binding_files(directory=None):
+    """Relative paths of the files a library directory is identified by: every Python and JSON file
+    of the package and the CUDA sources (build products and the binding file itself excluded)."""
+    root = Path(directory) if directory is not None else _PACKAGE
+    names = []
+    for path in sorted(root.rglob("*")):
+        rel = path.relative_to(root)
+        if not path.is_file() or rel.parts[0].startswith("native_") or "__pycache__" in rel.parts:
+            continue
+        if path.name != BINDING_NAME and path.suffix in (".py", ".json", ".cu", ".cuh"):
+            names.append(rel.as_posix())
+    return names
+
+
+def write_source_binding(directory=None):
+    """Write <directory>/SOURCE_BINDING.json = {complete, scope, files: {relative path: sha256}}, the
+    receipt `sdacc/diffusion_research/library.py:11-15` (`bind`) checks before it imports a library
+    directory.  Returns the receipt."""
+    root = Path(directory) if directory is not None else _PACKAGE
+    receipt = dict(complete=True, scope="source snapshot of the sm_100a library; build the native artefact locally "
+                                        "with build_native(<directory>/native_sm80)",
+                   files={name: sha(root / name) for name in source_binding_files(root)})
+    (root / BINDING_NAME).write_text(json.dumps(receipt, indent=2) + "\n")
+    return receipt
+
+
 def _declare(lib):
     c = ctypes
     vp, i64, i32 = c.c_void_p, c.c_int64, c.c_int

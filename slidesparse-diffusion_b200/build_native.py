@@ -28,10 +28,15 @@ def main():
     parser.add_argument("--output", type=Path, default=None,
                         help="directory for the library and its receipt (default: <package>/native_sm100a)")
     parser.add_argument("--force", action="store_true")
+    parser.add_argument("--binding", action="store_true",
+                        help="also write SOURCE_BINDING.json (file hashes) next to the package sources")
     args = parser.parse_args()
     sdk = load_package()
     receipt = sdk.build_native(args.output, arch=args.arch, force=args.force)
     print("Built native library", receipt["library_sha"][:16], "for", receipt["arch"])
+    if args.binding:
+        from slidesparse_diffusion_b200 import backend
+        print("Wrote", backend.BINDING_NAME, "over", len(backend.write_source_binding()["files"]), "files")
 
 
 if __name__ == "__main__":

@@ -28,6 +28,17 @@ _PLAN_FRONTENDS = ("graph_native", "graph_packed16", "graph1_native", "graph1_pa
                    "direct2_native", "direct2_packed16")
 FRONTENDS = _PLAIN_FRONTENDS + _PLAN_FRONTENDS + ("auto",)
 LAYOUT = "b200-v1"          # tag of this library's metadata word order, kept in identity / payloads
+# `kernel_source_sha` values of payloads written by the reference's packer (the hashes its own
+# `PackedLinear.load` accepts, sdacc/w8a8_slidesparse/runtime.py:236-238, plus its current
+# csrc/dualscale_sm80.cu): all of them store metadata in the SM80 kernel's word order, which
+# `load` converts.  A payload from any other packer is refused rather than guessed at.
+REFERENCE_PACKER_SHAS = frozenset((
+    "f27beddfed9f44b10a239772acc812f78cf78a999fbbeaea7ccd22f3a16c587f",
+    "2787082a7feed4f7d9287578f7b7cac80857770dc4d8d704cdf888dca4a625a4",
+    "e4af641f13175c73225ed6cc8e15a50c88de5d7454811151811081fa85551c61",
+    "33f19700a1d9e6e01390cdc19627837ecfdeca2fffdd45e65ca1e7e7cac0c12d",
+    "600cbf9ffdd7a863b9d04a0afdab6279caea70d3a705ea8cf92e26ab8c9f0b7a",
+))
 _TENSOR_KEYS = ("packed", "metadata", "scales", "bias")
 _PAYLOAD_VERSION = 1
 
@@ -243,10 +254,18 @@ class PackedLinear(torch.nn.Module):
             raise ValueError(f"payload version {payload.get('version')!r} is not supported")
         identity = dict(payload["identity"])
         metadata = payload["metadata"]
-        if identity.get("metadata_layout") == LAYOUT:
-            if identity.get("kernel_source_sha") is None:
+        layout, packer = identity.get("metadata_layout"), identity.get("kernel_source_sha")
+        if layout == LAYOUT:
+            # this library's word order; the hash is provenance only (the order is what the tag names,
+            # and the tag changes whenever the packed or metadata layout does)
+            if packer is None:
                 raise ValueError("the payload does not say which kernel source packed it")
+        elif layout is not None:
+            raise ValueError(f"unknown metadata layout {layout!r}: this library reads {LAYOUT!r} and the reference's payloads")
         else:
+            if packer not in REFERENCE_PACKER_SHAS:
+                raise ValueError("untagged payload from an unknown packer: its metadata order cannot be assumed "
+                                 f"(kernel_source_sha {packer!r})")
             from .importer import sm80_metadata_to_b200
             rows, half_width = payload["packed"].shape
             metadata = sm80_metadata_to_b200(metadata, rows, 2 * half_width)

@@ -46,43 +46,63 @@ def prepare_shard(qweight, scales, bias, mode, rank, world, members=None, **kwar
     return op, (start, end)
 
 
-def all_gather_columns(local, bounds, group=None):
-    """Gather [..., n_rank] shards into [..., n] on every rank (one all-gather; ragged shards are
-    padded to the widest one for the collective and trimmed afterwards)."""
+def gather_shards(local, bounds, group=None):
+    """One all-gather of this rank's [..., n_rank] shard: returns `[world, ..., widest]`, rank r's
+    shard in slot r (columns beyond its width are padding when the shards are ragged).  With equal
+    widths the collective reads the projection's output and writes the result tensor directly: no
+    staging copy on either side."""
     world = dist.get_world_size(group)
     if len(bounds) != world:
         raise ValueError("one channel range per rank required")
-    widths = [end - start for start, end in bounds]
-    widest = max(widths)
-    lead = local.shape[:-1]
+    widest = max(end - start for start, end in bounds)
     send = local
     if local.shape[-1] != widest:
-        send = local.new_zeros((*lead, widest))
+        send = local.new_zeros((*local.shape[:-1], widest))
         send[..., :local.shape[-1]] = local
     send = send.contiguous()
     if dist.get_backend(group) == "nccl":
-        gathered = local.new_empty((world, *lead, widest))
+        gathered = local.new_empty((world, *send.shape))
         dist.all_gather_into_tensor(gathered, send, group=group)
-        parts = [gathered[r] for r in range(world)]
-    else:
-        parts = [torch.empty_like(send) for _ in range(world)]
-        dist.all_gather(parts, send, group=group)
-    return torch.cat([parts[r][..., :widths[r]] for r in range(world)], dim=-1)
+        return gathered
+    parts = [torch.empty_like(send) for _ in range(world)]
+    dist.all_gather(parts, send, group=group)
+    return torch.stack(parts)
+
+
+def all_gather_columns(local, bounds, group=None):
+    """Gather [..., n_rank] shards into one row-major [..., n] tensor on every rank: the all-gather
+    of `gather_shards` plus ONE re-ordering copy (shard-major -> row-major)."""
+    gathered = gather_shards(local, bounds, group)
+    widths = [end - start for start, end in bounds]
+    world, widest = gathered.shape[0], gathered.shape[-1]
+    if all(w == widest for w in widths):
+        return gathered.movedim(0, -2).reshape(*gathered.shape[1:-1], world * widest)
+    return torch.cat([gathered[r][..., :widths[r]] for r in range(world)], dim=-1)
 
 
 class TensorParallelProjection(torch.nn.Module):
-    """N-split tensor-parallel projection: local column shard + all-gather of the BF16 outputs."""
+    """N-split tensor-parallel projection: local column shard + one NCCL all-gather of the BF16 outputs.
+
+    `layout="rows"` (default) returns the row-major [..., N] tensor a dense layer would (one extra
+    copy after the collective).  `layout="shards"` returns the collective's own result
+    [world, ..., N / world] without that copy: the natural form for a consumer that splits the
+    channels anyway (attention heads: shard r holds heads r * H / world ...), and what the N-split
+    variant costs at its best with NCCL."""
 
     def __init__(self, shard, bounds, group=None):
         super().__init__()
         self.shard, self.bounds, self.group = shard, list(bounds), group
         self.n = self.bounds[-1][1]
 
-    def forward(self, x, output_addend=None):
+    def forward(self, x, output_addend=None, layout="rows"):
+        if layout not in ("rows", "shards"):
+            raise ValueError("layout is 'rows' or 'shards'")
         rank = dist.get_rank(self.group)
         start, end = self.bounds[rank]
         addend = None if output_addend is None else output_addend[..., start:end]
         local = self.shard(x) if addend is None else self.shard(x, output_addend=addend)
+        if layout == "shards":
+            return gather_shards(local, self.bounds, self.group)
         return all_gather_columns(local, self.bounds, self.group)
 
 

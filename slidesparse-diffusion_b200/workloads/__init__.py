@@ -8,6 +8,7 @@ alias list resolves to the same (M, K, N, members, recipe).
 """
 from ..composite import ProtectedFFNOutput, SharedProjection
 from ..packing import group_size
+from ..profile import selectable
 from ..runtime import PackedLinear
 
 # hidden width, MLP width, image tokens (CFG batch included), text tokens, family
@@ -87,6 +88,11 @@ def prepare_for(workload, module, qweight, scales, bias=None, mode="2:4", attent
     length = group_size(mode)
     if execution not in ("default", "recommended"):
         raise ValueError("unknown execution recipe")
+    # the reference refuses groups whose measured sparse projection did not beat dense
+    # (`workloads/__init__.py:17`); here the rule is profile.selectable, from this GPU's measurements
+    if not selectable(length, group["m"], group["k"], group["n"]):
+        raise ValueError(f"{workload}/{module} ({group['m']}x{group['k']}->{group['n']}) is not faster than the dense "
+                         "projection on this GPU; keep Dense")
     if tuple(qweight.shape) != (group["n"], group["k"]):
         raise ValueError("weight shape differs from frozen workload")
     packed = PackedLinear.prepare(qweight, scales, bias, length)

@@ -212,11 +212,11 @@ def test_workload_inventory(sdk, oracle):
     assert workloads.shapes("pixart_sigma512")["text.cross-KV"] == dict(
         m=600, k=1152, n=2304, members=[1152, 1152], recipe="ordinary", row_stride=1152, slice_start=0)
     assert len({(w, m) for w in workloads.MODELS for m in workloads.shapes(w)}) >= 55
-    qweight, scales = oracle.make_weight(2304, 1152, 6, seed=0)
-    op = workloads.prepare_for("pixart_sigma512", "text.cross-KV", torch.from_numpy(qweight), torch.from_numpy(scales), mode="4:6")
-    assert isinstance(op, sdk.SharedProjection) and op.widths == (1152, 1152)
+    qweight, scales = oracle.make_weight(3456, 1152, 6, seed=0)
+    op = workloads.prepare_for("pixart_sigma512", "image.QKV", torch.from_numpy(qweight), torch.from_numpy(scales), mode="4:6")
+    assert isinstance(op, sdk.SharedProjection) and op.widths == (1152, 1152, 1152)
     with pytest.raises(ValueError):
-        workloads.prepare_for("pixart_sigma512", "image.cross-Q", torch.from_numpy(qweight), torch.from_numpy(scales))
+        workloads.prepare_for("pixart_sigma512", "image.FFN-in", torch.from_numpy(qweight), torch.from_numpy(scales))
     from slidesparse_diffusion_b200.workloads import pixart_sigma512
     assert pixart_sigma512.WORKLOAD == "pixart_sigma512"
 
@@ -229,3 +229,30 @@ def test_missing_library_fails_loudly(sdk, tmp_path):
     (tmp_path / backend.LIBRARY_NAME).write_bytes(b"")
     with pytest.raises(ValueError):
         backend.load_native(tmp_path)
+
+
+def test_load_refuses_payloads_of_unknown_origin(sdk, oracle, tmp_path):
+    """An untagged payload is only converted if the reference's packer wrote it; an unknown layout
+    tag is refused (the reference's load checks the hash too, runtime.py:236-238 there)."""
+    op, _, _ = make_op(sdk, oracle)
+    path = tmp_path / "op.pt"
+    op.save(path)
+    blob = torch.load(path, weights_only=True)
+    for identity in (dict(kernel_source_sha="0" * 64), dict(), dict(metadata_layout="b200-v0", kernel_source_sha="x"),
+                     dict(metadata_layout="b200-v1")):
+        torch.save(dict(blob, identity=identity), path)
+        with pytest.raises(ValueError):
+            sdk.PackedLinear.load(path)
+
+
+def test_prepare_for_keeps_unprofitable_groups_dense(sdk, oracle):
+    """workloads.prepare_for refuses a group the profile would not select, as the reference does for
+    groups that failed its acceleration gate (workloads/__init__.py:17 there)."""
+    from slidesparse_diffusion_b200 import workloads, profile
+    assert not profile.selectable(8, 600, 1152, 2304) and profile.selectable(4, 2048, 1152, 4608)
+    qweight, scales = oracle.make_weight(2304, 1152, 8, seed=0)
+    with pytest.raises(ValueError, match="keep Dense"):
+        workloads.prepare_for("pixart_sigma512", "text.cross-KV", torch.from_numpy(qweight), torch.from_numpy(scales), mode="6:8")
+    qweight, scales = oracle.make_weight(4608, 1152, 4, seed=0)
+    op = workloads.prepare_for("pixart_sigma512", "image.FFN-in", torch.from_numpy(qweight), torch.from_numpy(scales))
+    assert isinstance(op, sdk.PackedLinear) and (op.k, op.n) == (1152, 4608)

@@ -56,6 +56,14 @@ def _worker(rank, world, port, results):
         got = y.view(torch.int16).numpy().view(np.uint16)
         assert np.array_equal(got, full["out_bits"]), "gathered shards differ from the unsharded projection"
 
+        # the collective's own layout: [world, m, widest], rank r's columns in slot r
+        shards = tp(x, layout="shards")
+        widest = max(e - b for b, e in bounds)
+        assert shards.shape == (world, m, widest)
+        for r, (b, e) in enumerate(bounds):
+            assert np.array_equal(shards[r][:, :e - b].contiguous().view(torch.int16).numpy().view(np.uint16),
+                                  full["out_bits"][:, b:e])
+
         addend = (torch.arange(m * n, dtype=torch.float32).reshape(m, n) / 997).to(torch.bfloat16)
         y2 = tp(x, output_addend=addend)
         expect = oracle.epilogue(full["acc"], full["sa"], scales, bias, addend)

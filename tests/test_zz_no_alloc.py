@@ -43,6 +43,18 @@ def run_both(backend, oracle, m, k, n, mode, seed):
                                   n, pn, ptr(got), n, stream)
     assert rc == 0, lib.ss_last_error().decode()
     torch.cuda.synchronize()
+    # From the second call on nothing may be allocated: neither through torch's allocator nor
+    # behind it (the driver's free-memory figure must not move either).
+    again = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    torch.cuda.synchronize()
+    torch_before, (free_before, _) = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()
+    rc = lib.ss_projection_static(ptr(x), x.stride(0), m, k, mode, ptr(packed), ptr(meta), ptr(sw), ptr(b),
+                                  n, pn, ptr(again), n, stream)
+    assert rc == 0, lib.ss_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == torch_before
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.equal(again.view(torch.int16), got.view(torch.int16))
     a = got.view(torch.int16).cpu().numpy()
     e = expect.view(torch.int16).cpu().numpy()
     assert not np.isnan(got.float().cpu().numpy()).any()
