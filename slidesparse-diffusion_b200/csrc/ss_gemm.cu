@@ -64,18 +64,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
-__device__ __forceinline__ bool mbar_peek(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok)
-      : "r"(ptx::smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
 // Dequantise one 32-token chunk held in registers (lane = channel) and store it.  sa_lane is the
 // scale of token tok_base + lane; the lanes hand each other the scale of the token being written.
 template <bool INT32_OUT, bool HAS_ADDEND>

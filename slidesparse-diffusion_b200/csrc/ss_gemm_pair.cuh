@@ -1,5 +1,5 @@
 // CTA-pair variant of the sparse GEMM (tcgen05 cta_group::2).  Included by ss_gemm.cu inside
-// namespace ss::{anonymous}, after KernelArgs, smem_desc, mbar_peek and store_chunk.
+// namespace ss::{anonymous}, after KernelArgs, smem_desc and store_chunk.
 //
 // Why a pair: the single-CTA kernel is bound by shared-memory bandwidth, not by the tensor
 // pipe.  A K=64 sparse INT8 MMA of M=128 x N reads 4 KB of A and 64*N bytes of B from shared
@@ -179,7 +179,10 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kBarStride; ++s) {
-      ptx::mbar_init(&bar_full[s], 1);
+      // a stage is ready when its operands have landed (the producer's arrival + the bytes) and, with
+      // a metadata warp, when its metadata has been copied into TMEM (that warp's commit): one
+      // barrier, so that the MMA thread polls once per stage
+      ptx::mbar_init(&bar_full[s], meta_warp ? 2 : 1);
       ptx::mbar_init(&bar_empty[s], 1);
       ptx::mbar_init(&bar_meta[s], 1);
       ptx::mbar_init(&bar_e[s], 1);
@@ -309,7 +312,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
       const bool odd_tail = (args.num_kb % KB) != 0;       // the last stage of a tile holds one block only
       uint32_t phase = 0, acc_it = 0;
-      bool ok = true, ready = false;
+      bool ok = true;
       // diagnostics (ss_micro_pair_rate): cluster 0 reports the cycles its tile loop took; bit 0 of
       // args.debug leaves the MMAs out (commits only), so that the operand feed is timed alone
       const bool probe = args.probe != nullptr && pair == 0;
@@ -350,11 +353,10 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
         for (int slot = 0; slot < kRing; ++slot) {
           SS_PF_BEGIN();
-          if (!ready && !ptx::mbar_wait(&bar_full[slot], phase, args.wait_ns)) { ok = false; more = false; break; }
-          // the stage's metadata: copied into TMEM by the metadata warp (done long before the operands
-          // have landed), or still to be copied by this thread
+          if (!ptx::mbar_wait(&bar_full[slot], phase, args.wait_ns)) { ok = false; more = false; break; }
           if constexpr (!RES) {
-            if (!ptx::mbar_wait(meta_warp ? &bar_meta[slot] : &bar_e[slot], phase, args.wait_ns)) { ok = false; more = false; break; }
+            // without a metadata warp this thread copies the stage's metadata itself (below)
+            if (!meta_warp && !ptx::mbar_wait(&bar_e[slot], phase, args.wait_ns)) { ok = false; more = false; break; }
           }
           SS_PF(pf_ready);
           if (st == 0) SS_TL(1, tl, 2);
@@ -393,9 +395,6 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           // stage's arrival.
           ptx::tc_commit_pair(&bar_empty[slot], 3);
           SS_PF(pf_commit);
-          // a look at the next stage's barrier once this stage's work is queued: it has usually
-          // completed by now, and a successful look is far cheaper than a wait
-          ready = mbar_peek(&bar_full[(slot + 1) % kRing], slot == kRing - 1 ? phase ^ 1u : phase);
           if (slot == kRing - 1) phase ^= 1u;
           SS_PF(pf_peek);
           if (++st == num_st) {
@@ -453,7 +452,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             for (int h = 0; h < nkb; ++h)
               ptx::tc_cp_128x128b_pair(e_tmem + 4 * h, smem_desc(e_addr + h * T::kEBlock, 128, 128, 0));
           }
-          ptx::tc_commit_pair(&bar_meta[s], 1);      // arrives (rank 0 only) when the copy has completed
+          ptx::tc_commit_pair(&bar_full[s], 1);      // arrives (rank 0 only) when the copy has completed
           if (++s == static_cast<uint32_t>(kRing)) { s = 0; phase ^= 1u; }
         }
       }
@@ -566,14 +565,14 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               const uint32_t* r = f + 16 * h + 4 * g;
 #pragma unroll
               for (int ab = 0; ab < 2; ++ab) {
+                // two tokens of one channel at a time with the packed FP32 instructions: each half is
+                // the same IEEE multiply / fused multiply-add (round to nearest) as the scalar form
                 const float w = sw[2 * h + ab], b = bias[2 * h + ab];
-                float y0 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab])), __fmul_rn(s.x, w), b);
-                float y1 = __fmaf_rn(__int2float_rn(static_cast<int32_t>(r[2 * ab + 1])), __fmul_rn(s.y, w), b);
-                if constexpr (GATED) {
-                  y0 = __fmul_rn(gate[2 * h + ab], y0);
-                  y1 = __fmul_rn(gate[2 * h + ab], y1);
-                }
-                const __nv_bfloat162 p = __floats2bfloat162_rn(y0, y1);     // low half = even token
+                const float2 acc = make_float2(__int2float_rn(static_cast<int32_t>(r[2 * ab])),
+                                               __int2float_rn(static_cast<int32_t>(r[2 * ab + 1])));
+                float2 y = __ffma2_rn(acc, __fmul2_rn(s, make_float2(w, w)), make_float2(b, b));
+                if constexpr (GATED) y = __fmul2_rn(make_float2(gate[2 * h + ab], gate[2 * h + ab]), y);
+                const __nv_bfloat162 p = __floats2bfloat162_rn(y.x, y.y);   // low half = even token
                 packed[2 * gi + ab] = *reinterpret_cast<const uint32_t*>(&p);
               }
             }

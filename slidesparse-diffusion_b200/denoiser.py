@@ -474,13 +474,19 @@ class DenoiseLoop:
             self.prev_x0.copy_(keep[1])
         self.graph.replay()
 
-    @torch.no_grad()
-    def run(self, seed=0, steps=None):
-        """Full sampling loop from seeded noise; returns the final latent (fp32)."""
+    def inputs(self, seed=0):
+        """(initial latent noise, conditioning) for `run`, drawn on the host from `seed` and moved to
+        the device: callers that time the loop draw them beforehand and pass them to `run`."""
         gen = torch.Generator(device="cpu").manual_seed(seed)
-        self.x.copy_(torch.randn(self.x.shape, generator=gen))
+        return torch.randn(self.x.shape, generator=gen).to(self.x.device), self.conditioning(seed)
+
+    @torch.no_grad()
+    def run(self, seed=0, steps=None, inputs=None):
+        """Full sampling loop from seeded noise (or from `inputs` = what `inputs(seed)` returned);
+        returns the final latent (fp32)."""
+        noise, cond = self.inputs(seed) if inputs is None else inputs
+        self.x.copy_(noise)
         self.prev_x0.zero_()
-        cond = self.conditioning(seed)
         if self.cond is None:
             self.cond = cond
         elif isinstance(cond, tuple):
