@@ -57,9 +57,9 @@ SAMPLE_TOKENS = 48            # rows per projection in the CPU sample (M = 1536 
 # DRAM traffic of the GEMM kernel divided by its algorithmic bytes, from the committed ncu capture of
 # three M=4096 launches (profiles/sparse_gemm_pair_kernel_flux_M4096.md): dram__bytes_read plus the
 # output size (each output byte is written once; part of it is still in L2 when the kernel's
-# counters stop) = 158.4 / 142.7 / 123.0 MB against 149.1 / 123.9 / 121.0 MB algorithmic; the bench
+# counters stop) = 116.6 / 161.9 / 158.3 MB against 116.0 / 149.1 / 123.9 MB algorithmic; the bench
 # scales the average algorithmic bytes per launch of its step by it
-TRAFFIC_OVER_ALGORITHMIC = (158.4 + 142.7 + 123.0) / (149.1 + 123.9 + 121.0)
+TRAFFIC_OVER_ALGORITHMIC = (116.6 + 161.9 + 158.3) / (116.0 + 149.1 + 123.9)
 
 
 def logical_ops(tokens=TOKENS):
@@ -517,12 +517,16 @@ def denoise_legs(torch, dist, name, device, rank, world, steps, warmup, images=1
             sparse_compiled_small = timed(loop, count)
             small.fuse_neighbours(True)
             sparse_fused_small = timed(denoiser.DenoiseLoop(small, graph=True, images=images), count)
+            loop = denoiser.DenoiseLoop(small, graph=True, images=images)
+            loop.model = torch.compile(small, fullgraph=True, dynamic=False)
+            sparse_fused_compiled_small = timed(loop, count)
             compiled = {"blocks": compiled_blocks, "eager_ms": eager_small, "compiled_ms": compiled_small,
                         "compiled_over_eager": ratio, "compile_seconds": time.time() - t0,
                         "full_depth_estimate_ms": dense_ms * ratio,
                         "sparse_pytorch_neighbours_ms": sparse_eager_small, "sparse_compiled_ms": sparse_compiled_small,
                         "sparse_fused_neighbours_ms": sparse_fused_small,
-                        "speedup_both_compiled": compiled_small / sparse_compiled_small,
+                        "sparse_fused_neighbours_compiled_ms": sparse_fused_compiled_small,
+                        "speedup_both_compiled": compiled_small / min(sparse_compiled_small, sparse_fused_compiled_small),
                         "what": f"torch.compile(fullgraph=True) of a {compiled_blocks}-block instance of the model, dense and "
                                 "sparse; the dense ratio is applied to the full-depth eager time"}
             del small, loop

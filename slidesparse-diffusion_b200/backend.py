@@ -502,7 +502,26 @@ def projection_fused(input, prologue, packed, metadata, scales, bias, group, n, 
     """`projection` with the prologue applied to the input inside the front-end kernel.
 
     With `gate` (BF16 [batch, n]) and `residual` (BF16 [batch, rows, n], contiguous) the result is
-    accumulated in place: residual += bf16(gate[b] * y), and `residual` is returned."""
+    accumulated in place: residual += bf16(gate[b] * y), and `residual` is returned.
+
+    Goes through the `slidesparse_b200::projection_fused` / `::projection_fused_accumulate_`
+    operators (registered with fake kernels), so a model that uses fused neighbours still traces
+    under `torch.compile(fullgraph=True)`."""
+    ops = torch.ops.slidesparse_b200
+    code = PROLOGUES[prologue.kind]
+    if gate is not None:
+        if residual is None or output_addend is not None:
+            raise ValueError("gated accumulation needs [batch, rows, k] input, a residual and no addend")
+        ops.projection_fused_accumulate_(residual, input, code, prologue.shift, prologue.scale, prologue.eps,
+                                         packed, metadata, scales, bias, int(group), int(n), gate)
+        return residual
+    return ops.projection_fused(input, code, prologue.shift, prologue.scale, prologue.eps, packed, metadata, scales,
+                                bias, int(group), int(n), output_addend)
+
+
+def _projection_fused_impl(input, prologue, packed, metadata, scales, bias, group, n, output_addend=None,
+                           gate=None, residual=None):
+    """The ctypes call behind the fused-projection operators."""
     if not input.is_cuda or input.dtype != torch.bfloat16 or input.ndim < 1:
         raise ValueError("BF16 CUDA input required")
     group = group_size(int(group))
@@ -708,3 +727,35 @@ def _register_ops():
     @torch.library.register_fake("sdacc_prepared_projection_sm80::run")
     def _fake_prepared(x, handle, n):
         return x.new_empty((*x.shape[:-1], n))
+
+    # additions of this library (no counterpart in the reference): the projection with element-wise
+    # neighbours fused in, as operators so that callers using them can still be compiled
+    own = Library("slidesparse_b200", "DEF")
+    weights = "Tensor packed,Tensor metadata,Tensor scales,Tensor bias,int group,int n"
+    pro = "int prologue,Tensor? shift,Tensor? scale,float eps"
+    own.define(f"projection_fused(Tensor input,{pro},{weights},Tensor? output_addend=None)->Tensor")
+    own.define(f"projection_fused_accumulate_(Tensor(a!) residual,Tensor input,{pro},{weights},Tensor gate)->()")
+
+    def _prologue_of(code, shift, scale, eps):
+        kind = {v: k for k, v in PROLOGUES.items()}[int(code)]
+        return Prologue(kind, shift, scale, eps)
+
+    def _op_fused(input, prologue, shift, scale, eps, packed, metadata, scales, bias, group, n, output_addend=None):
+        return _projection_fused_impl(input, _prologue_of(prologue, shift, scale, eps), packed, metadata, scales, bias,
+                                      group, n, output_addend)
+
+    def _op_fused_accumulate(residual, input, prologue, shift, scale, eps, packed, metadata, scales, bias, group, n, gate):
+        _projection_fused_impl(input, _prologue_of(prologue, shift, scale, eps), packed, metadata, scales, bias, group, n,
+                               None, gate, residual)
+
+    own.impl("projection_fused", _op_fused, "CUDA")
+    own.impl("projection_fused_accumulate_", _op_fused_accumulate, "CUDA")
+    _libraries.append(own)
+
+    @torch.library.register_fake("slidesparse_b200::projection_fused")
+    def _fake_fused(input, prologue, shift, scale, eps, packed, metadata, scales, bias, group, n, output_addend=None):
+        return input.new_empty((*input.shape[:-1], n))
+
+    @torch.library.register_fake("slidesparse_b200::projection_fused_accumulate_")
+    def _fake_fused_accumulate(residual, input, prologue, shift, scale, eps, packed, metadata, scales, bias, group, n, gate):
+        return None

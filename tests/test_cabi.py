@@ -119,3 +119,30 @@ def test_launch_entries_validate_before_touching_the_gpu(backend):
     assert lib.ss_gemm_int32(dummy, dummy, dummy, dummy, 40, 1, 32, 32, 128, None) == backend.SS_E_ARG    # m > pm
     assert lib.ss_plan_run(12345, dummy, 8, None, None, dummy, 8, None) == backend.SS_E_HANDLE
     assert lib.ss_plan_release(12345) == 0
+
+
+def test_tuning_switches_round_trip_on_the_host(backend):
+    """ss_set_option / ss_get_option need no GPU: the switches live in host memory."""
+    assert backend.get_option("token_tile") == 0 and backend.get_option("resident") == 1
+    assert backend.get_option("wait_ns") == 2_000_000_000
+    for name, value in (("token_tile", 240), ("store", 0), ("meta_warp", 1), ("wait_ns", 7_000_000)):
+        previous = backend.set_option(name, value)
+        assert backend.get_option(name) == value
+        backend.set_option(name, previous)
+        assert backend.get_option(name) == previous
+    lib = backend.library()
+    assert lib.ss_set_option(b"no_such_switch", 1) == backend.SS_E_ARG and b"no_such_switch" in lib.ss_last_error()
+    assert lib.ss_set_option(b"wait_ns", 0) == backend.SS_E_ARG
+    assert lib.ss_get_option(b"pdl", None) == backend.SS_E_ARG
+
+
+def test_diagnostic_entries_validate_before_touching_the_gpu(backend):
+    lib = backend.library()
+    elapsed = ctypes.c_int64()
+    assert lib.ss_micro_wait_limit(0, ctypes.byref(elapsed)) == backend.SS_E_ARG
+    assert lib.ss_micro_wait_limit(10 ** 12, ctypes.byref(elapsed)) == backend.SS_E_ARG          # beyond 100 ms
+    assert lib.ss_micro_wait_limit(1000, None) == backend.SS_E_ARG
+    cycles, stages = ctypes.c_double(), ctypes.c_int64()
+    assert lib.ss_micro_pair_rate(256, 256, 100, 0, 0, ctypes.byref(cycles), ctypes.byref(stages)) == backend.SS_E_ARG
+    assert lib.ss_micro_pair_rate(256, 256, 256, 0, 8, ctypes.byref(cycles), ctypes.byref(stages)) == backend.SS_E_ARG
+    assert lib.ss_gemm_resources(4096, 4608, 1152, None, 8) == backend.SS_E_ARG

@@ -22,12 +22,14 @@ def nrmse(actual, expected):
     return float((actual.float() - expected.float()).norm() / expected.float().norm().clamp_min(1e-12))
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("name", ["dit-xl-512", "sd35-large-512"])
-def test_fullgraph_compile_traces_through_the_projection_operators(sdk, backend, name):
+def test_fullgraph_compile_traces_through_the_projection_operators(sdk, backend, name, fused):
     from torch._inductor.compile_fx import compile_fx
     denoiser, model = tiny_model(name, steps=2)
     mode = model.pack(only_profitable=False)
     model.select(mode)
+    model.fuse_neighbours(fused)       # fused neighbours go through this library's own operators
     spec = model.spec
     loop = denoiser.DenoiseLoop(model)
     cond = loop.conditioning(seed=3)
@@ -38,7 +40,7 @@ def test_fullgraph_compile_traces_through_the_projection_operators(sdk, backend,
 
     def inspecting_backend(gm, example_inputs):
         seen.append(sum(1 for node in gm.graph.nodes if node.op == "call_function"
-                        and "sdacc_mild_projection_sm80" in str(node.target)))
+                        and ("sdacc_mild_projection_sm80" in str(node.target) or "slidesparse_b200" in str(node.target))))
         return compile_fx(gm, example_inputs)
 
     with torch.no_grad():
