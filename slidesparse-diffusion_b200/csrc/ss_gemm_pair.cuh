@@ -590,7 +590,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           // the half chunk that ends a 240-token tile goes out through a 16-token box: the other 16
           // staged rows hold columns of the neighbouring accumulator and belong to the next tile
           const CUtensorMap* dst = (T::kHalfTail && c == T::kChunks - 1) ? &map_out_tail : &map_out;
-          if (ch_w < args.n) {
+          if (ch_w < args.n && !(args.debug & 4)) {
             if constexpr (GATED) {
               ptx::tma_reduce_add_2d(dst, stage, ch_w, tok0 + c * 32);
             } else if constexpr (MODE == kOutBf16TmaPeers) {
@@ -616,7 +616,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             const int c = half + kPairSub * i;
             ptx::tc_wait_ld();
             if (i + 1 < mine) load(f[(i + 1) & 1], c + kPairSub); else release();
-            emit(f[i & 1], c, sa_mine[i]);
+            if (!(args.debug & 8)) emit(f[i & 1], c, sa_mine[i]);
           }
         }
       }

@@ -103,6 +103,21 @@ def test_weights_resident_form_is_exact(backend, oracle, oracle_c, mode, m, k, n
     assert backend.device_status() == 0
 
 
+@pytest.mark.parametrize("meta_warp,wide_cp", [(0, 1), (0, 0), (1, 0)])
+def test_metadata_copy_variants_are_exact(backend, oracle, oracle_c, meta_warp, wide_cp):
+    """The switches that decide who copies a stage's metadata into TMEM (the metadata warp or the
+    MMA thread) and how (one 128x256b copy or two 128x128b): same bits in every combination, odd and
+    even numbers of 128-column blocks."""
+    for k in (640, 1536):                                   # 6:8 -> 1024 (8 blocks) / 2304 lifted columns (18 blocks); 4:6 of 640 -> 7 blocks
+        for mode in (8, 6):
+            case = prepare_case(oracle, 1000, k, 520, mode, seed=k + mode)
+            with option(backend, "meta_warp", meta_warp), option(backend, "wide_cp", wide_cp), option(backend, "resident", 0):
+                out = c_gemm_run(backend, dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32),
+                                 dev(case["sa"]), dev(case["scales"]), dev(case["bias"]), 1000, 520)
+            assert np.array_equal(bits(out), oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"]))
+    assert backend.device_status() == 0
+
+
 @pytest.mark.parametrize("tile", [224, 240, 256])
 def test_large_token_tiles_full_height(backend, oracle, oracle_c, tile):
     """Several complete token tiles per cluster (so both accumulators and the half chunk of the
