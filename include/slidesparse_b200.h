@@ -209,6 +209,8 @@ int ss_projection_peers(const void* x_bf16, int64_t x_row_stride, int64_t m, int
  * that cluster 0 needed for its whole tile loop, with parts of the kernel switched off:
  *   flags bit 0  no MMAs are issued (commits only): the shared-memory feed from L2 alone
  *   flags bit 1  the epilogue hands every accumulator straight back: the main loop alone
+ *   flags bit 2  the epilogue runs but does not issue its TMA stores (the output stays unwritten)
+ *   flags bit 3  the epilogue only loads the accumulator from TMEM (no math, staging or stores)
  * token_tile 0 lets the library choose (including the weights-resident form); 128 / 192 / 224 /
  * 240 / 256 force a tile.  Allocates and frees its operands with cudaMalloc and synchronises the
  * device.  This is how the ceiling of the main loop's dataflow is measured, as opposed to argued. */

@@ -389,11 +389,11 @@ def micro_mma_rate(token_tile, sparse=True, with_metadata_copy=False, iterations
     return value.value
 
 
-def micro_pair_rate(m, n, pk, token_tile=0, no_mma=False, no_epilogue=False):
+def micro_pair_rate(m, n, pk, token_tile=0, no_mma=False, no_epilogue=False, no_stores=False, loads_only=False):
     """(cycles per 256-column pipeline stage, stages) of cluster 0 of the real GEMM kernel on scratch
     operands of this size, optionally without its MMAs and / or its epilogue work (diagnostic)."""
     cycles, stages = ctypes.c_double(), ctypes.c_int64()
-    check(library().ss_micro_pair_rate(int(m), int(n), int(pk), int(token_tile), int(bool(no_mma)) | 2 * int(bool(no_epilogue)),
+    check(library().ss_micro_pair_rate(int(m), int(n), int(pk), int(token_tile), int(bool(no_mma)) | 2 * int(bool(no_epilogue)) | 4 * int(bool(no_stores)) | 8 * int(bool(loads_only)),
                                        ctypes.byref(cycles), ctypes.byref(stages)))
     return cycles.value, stages.value
 

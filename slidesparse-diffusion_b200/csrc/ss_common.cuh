@@ -103,7 +103,8 @@ struct GemmArgs {
   const void* peer_out[8] = {};
   int peer_count = 0;
   // diagnostics (ss_micro.cu): wait limit of this launch (0 = the library's), kernel parts switched
-  // off (bit 0 the MMAs, bit 1 the epilogue work), and where cluster 0 reports {cycles, stages}
+  // off (bit 0 the MMAs, 1 the epilogue work, 2 its TMA stores, 3 all but its TMEM loads), and where
+  // cluster 0 reports {cycles, stages}
   unsigned long long wait_ns = 0;
   int debug = 0;
   unsigned long long* probe = nullptr;

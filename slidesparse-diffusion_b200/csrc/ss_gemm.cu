@@ -50,7 +50,7 @@ struct KernelArgs {
   int res_stages;       // weights-resident form: activation pipeline stages
   int peer_count;       // tensor-parallel form: number of destination tensor maps
   unsigned long long wait_ns;      // limit of every mbarrier wait
-  int debug;                       // diagnostics: bit 0 no MMAs, bit 1 no epilogue work
+  int debug;                       // diagnostics: bit 0 no MMAs, 1 no epilogue work, 2 no TMA stores, 3 TMEM loads only
   unsigned long long* probe;       // diagnostics: cluster 0 writes {cycles of its tile loop, stages}
 };
 

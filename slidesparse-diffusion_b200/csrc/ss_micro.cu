@@ -146,7 +146,7 @@ extern "C" int ss_micro_pair_rate(int64_t m, int64_t n, int64_t pk, int token_ti
   SS_REQUIRE(cycles_per_stage && stages, SS_E_ARG, "pair rate: result pointers required");
   SS_REQUIRE(m > 0 && n > 0 && pk > 0 && pk % 128 == 0 && m <= 65536 && n <= 65536 && pk <= 65536, SS_E_ARG,
              "pair rate: sizes must be positive, pk a multiple of 128, each at most 65536");
-  SS_REQUIRE((flags & ~15) == 0, SS_E_ARG, "pair rate: flags are bit 0 (no MMAs) and bit 1 (no epilogue)");
+  SS_REQUIRE((flags & ~15) == 0, SS_E_ARG, "pair rate: flags are bits 0..3 (no MMAs, no epilogue, no TMA stores, TMEM loads only)");
   const int64_t pm = ceil_to(m, 32), pn = ceil_to(n, 32);
   const size_t q_bytes = static_cast<size_t>(pm) * pk, a_bytes = static_cast<size_t>(pn) * pk / 2;
   const size_t e_bytes = static_cast<size_t>(pn) * pk / 8, o_bytes = static_cast<size_t>(m) * pn * 2;

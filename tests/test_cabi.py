@@ -144,5 +144,5 @@ def test_diagnostic_entries_validate_before_touching_the_gpu(backend):
     assert lib.ss_micro_wait_limit(1000, None) == backend.SS_E_ARG
     cycles, stages = ctypes.c_double(), ctypes.c_int64()
     assert lib.ss_micro_pair_rate(256, 256, 100, 0, 0, ctypes.byref(cycles), ctypes.byref(stages)) == backend.SS_E_ARG
-    assert lib.ss_micro_pair_rate(256, 256, 256, 0, 8, ctypes.byref(cycles), ctypes.byref(stages)) == backend.SS_E_ARG
+    assert lib.ss_micro_pair_rate(256, 256, 256, 0, 16, ctypes.byref(cycles), ctypes.byref(stages)) == backend.SS_E_ARG
     assert lib.ss_gemm_resources(4096, 4608, 1152, None, 8) == backend.SS_E_ARG
