@@ -215,6 +215,31 @@ def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+class _on_device:
+    """`with torch.cuda.device(d)` that does nothing when d is already current (the common case:
+    the switch costs several microseconds of host time per call)."""
+
+    def __init__(self, device):
+        self.guard = None if device.index == torch.cuda.current_device() else torch.cuda.device(device)
+
+    def __enter__(self):
+        if self.guard is not None:
+            self.guard.__enter__()
+
+    def __exit__(self, *exc):
+        if self.guard is not None:
+            self.guard.__exit__(*exc)
+
+
+def _scratch(pm, pk, device):
+    """Front-end output handed to the GEMM inside one projection call: q [pm, pk] and sa [pm] carved
+    from ONE allocation (sa first: 4*pm is a multiple of 128 bytes, so q stays 16-byte aligned).
+    Returns (owner tensor, q pointer, sa pointer)."""
+    owner = torch.empty(4 * pm + pm * pk, dtype=torch.uint8, device=device)
+    base = owner.data_ptr()
+    return owner, ctypes.c_void_p(base + 4 * pm), ctypes.c_void_p(base)
+
+
 def _check_config(config):
     if config not in VALID_CONFIGS:
         raise ValueError("invalid config")
@@ -348,14 +373,13 @@ def _projection(input, packed, metadata, scales, bias, group, n, config, output_
     addend = output_addend
     if addend is not None:
         addend = _check_addend(addend.reshape(-1, n), input.device, m, n)
-    q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
-    sa = torch.empty(pm, dtype=torch.float32, device=input.device)
+    owner, q_ptr, sa_ptr = _scratch(pm, pk, input.device)
     out = torch.empty((*input.shape[:-1], n), dtype=torch.bfloat16, device=input.device)
-    with torch.cuda.device(input.device):
+    with _on_device(input.device):
         check(library().ss_projection(_ptr(flat), flat.stride(0), m, k, group, _ptr(packed), _ptr(metadata),
                                       _ptr(scales), _ptr(bias), _ptr(addend),
                                       addend.stride(0) if addend is not None else 0, n, pn,
-                                      _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
+                                      q_ptr, sa_ptr, _ptr(out), n, _stream(input.device)))
     return out
 
 
@@ -554,14 +578,13 @@ def _projection_fused_impl(input, prologue, packed, metadata, scales, bias, grou
         out = residual
     else:
         out = torch.empty((*input.shape[:-1], n), dtype=torch.bfloat16, device=input.device)
-    q = torch.empty((pm, pk), dtype=torch.int8, device=input.device)
-    sa = torch.empty(pm, dtype=torch.float32, device=input.device)
-    with torch.cuda.device(input.device):
+    owner, q_ptr, sa_ptr = _scratch(pm, pk, input.device)
+    with _on_device(input.device):
         check(library().ss_projection_fused(_ptr(flat), flat.stride(0), m, k, group, code, _ptr(shift), _ptr(scale),
                                             mod_stride, rows, eps, _ptr(packed), _ptr(metadata), _ptr(scales), _ptr(bias),
                                             _ptr(addend), addend.stride(0) if addend is not None else 0,
                                             _ptr(gate), gate_stride, n, pn,
-                                            _ptr(q), _ptr(sa), _ptr(out), n, _stream(input.device)))
+                                            q_ptr, sa_ptr, _ptr(out), n, _stream(input.device)))
     return out
 
 
