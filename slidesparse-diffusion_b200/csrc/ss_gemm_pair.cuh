@@ -42,7 +42,7 @@ __device__ long long g_timeline[kTlClusters * 3 * kTlTiles * kTlSlots];
       g_timeline[((pair * 3 + (role)) * kTlTiles + (tile_index)) * kTlSlots + (slot)] = clock64(); \
   } while (0)
 // per-cluster sums of the cycles the producer and the MMA thread spend in each kind of operation
-constexpr int kPfSlots = 16;
+constexpr int kPfSlots = 48;
 __device__ long long g_profile[kTlClusters * kPfSlots];
 #define SS_PF_BEGIN() long long pf_t = clock64()
 #define SS_PF(acc) do { const long long pf_n = clock64(); (acc) += pf_n - pf_t; pf_t = pf_n; } while (0)
@@ -53,6 +53,23 @@ __device__ long long g_profile[kTlClusters * kPfSlots];
 #define SS_PF(acc) do {} while (0)
 #define SS_PF_STORE(slot, value) do {} while (0)
 #endif
+
+// A cluster's position in its tile sequence (tile = token tile * tiles_ch2 + channel tile, advancing
+// by the cluster count), kept as the two tile indices so that no role divides once per tile: an
+// integer division by a run-time value is a chain of some 40 dependent instructions.
+struct TileWalk {
+  int tile, ch, tok;
+  int step, step_ch, step_tok, tiles_ch2;
+  __device__ __forceinline__ TileWalk(int first, int step_, int tiles_ch2_)
+      : tile(first), ch(first % tiles_ch2_), tok(first / tiles_ch2_),
+        step(step_), step_ch(step_ % tiles_ch2_), step_tok(step_ / tiles_ch2_), tiles_ch2(tiles_ch2_) {}
+  __device__ __forceinline__ void advance() {
+    tile += step;
+    ch += step_ch;
+    tok += step_tok;
+    if (ch >= tiles_ch2) { ch -= tiles_ch2; ++tok; }
+  }
+};
 
 template <int NT, int KB>
 struct PairTile {
@@ -244,9 +261,9 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
       ptx::grid_dep_wait();           // q is written by the kernel launched just before this one
-      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++tl) {
-        const int ch0 = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
-        const int tok0 = (tile / tiles_ch2) * NT + static_cast<int>(rank) * T::kHalf;
+      for (TileWalk w(tile_first, tile_step, tiles_ch2); w.tile < num_tiles && ok; w.advance(), ++tl) {
+        const int ch0 = w.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
+        const int tok0 = w.tok * NT + static_cast<int>(rank) * T::kHalf;
         SS_TL(0, tl, 0);
         for (int st = 0; st < num_st; ++st) {
           SS_PF_BEGIN();
@@ -476,37 +493,48 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const bool tl_warp = warp == 2 && lane == 0;
     constexpr int kMine = (T::kChunks + kPairSub - 1) / kPairSub;     // chunks per warp and tile, at most
     float sa_next[kMine], sw_next[4], bias_next[4];
-    auto prefetch = [&](int t) {
-      const int pch = (t % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane_ch;
-      const int ptok0 = (t / tiles_ch2) * NT;
+#ifdef SS_TIMELINE
+    long long pe_acc = 0, pe_ld = 0, pe_prep = 0, pe_math = 0, pe_fence = 0, pe_store = 0, pe_rest = 0, pe_chunks = 0, pe_commit = 0, pe_null = 0, pe_reconv = 0;
+#endif
+    // The scales of the next tile are fetched while this one is processed.  The loads must not be
+    // consumed where they are issued (a select on the loaded value would wait an L2 round trip
+    // here, once per tile): indices are clamped into range instead, and what a lane then holds
+    // for a token >= m or a channel >= n multiplies values that the stores clip.
 #pragma unroll
-      for (int i = 0; i < kMine; ++i) {
-        const int in_tile = (half + kPairSub * i) * 32 + lane;
-        sa_next[i] = (in_tile < NT && ptok0 + in_tile < args.m) ? __ldg(args.sa + ptok0 + in_tile) : 1.f;
-      }
+    for (int i = 0; i < 4; ++i) bias_next[i] = 0.f;
+    const int last_tok = args.m - 1, last_ch = args.n - 1;
+    TileWalk nxt(tile_first, tile_step, tiles_ch2);
+    auto prefetch = [&]() {
+      const int pch = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane_ch;
+      const int ptok = nxt.tok * NT + half * 32 + lane;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {               // channels lane_ch + 8 i of the warp's 32
-        const int c = pch + 8 * i;
-        sw_next[i] = c < args.n ? __ldg(args.sw + c) : 1.f;
-        bias_next[i] = (c < args.n && args.bias) ? __ldg(args.bias + c) : 0.f;
+      for (int i = 0; i < kMine; ++i) sa_next[i] = __ldg(args.sa + min(ptok + kPairSub * 32 * i, last_tok));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sw_next[i] = __ldg(args.sw + min(pch + 8 * i, last_ch));   // channels lane_ch + 8 i
+      if (args.bias) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) bias_next[i] = __ldg(args.bias + min(pch + 8 * i, last_ch));
       }
     };
     ptx::grid_dep_wait();             // sa is written by the kernel launched just before this one
-    if (tile_first < num_tiles) prefetch(tile_first);
-    for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it, ++tl) {
+    if (nxt.tile < num_tiles) prefetch();
+    for (; nxt.tile < num_tiles && ok; ++acc_it, ++tl) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
-      const int ch_w = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32;
-      const int tok0 = (tile / tiles_ch2) * NT;
+      const int ch_w = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32;
+      const int tok0 = nxt.tok * NT;
       float sa_mine[kMine], sw[4], bias[4];
 #pragma unroll
       for (int i = 0; i < kMine; ++i) sa_mine[i] = sa_next[i];
 #pragma unroll
       for (int i = 0; i < 4; ++i) { sw[i] = sw_next[i]; bias[i] = bias_next[i]; }
-      if (tile + tile_step < num_tiles) prefetch(tile + tile_step);
+      nxt.advance();
+      if (nxt.tile < num_tiles) prefetch();
       int chunks = (args.m - tok0 + 31) / 32;
       chunks = chunks < T::kChunks ? chunks : T::kChunks;
       if (tl_warp) SS_TL(2, tl, 0);
+      SS_PF_BEGIN();
       if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u, args.wait_ns)) { ok = false; break; }
+      SS_PF(pe_acc);
       if (tl_warp) SS_TL(2, tl, 1);
       ptx::tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * NT;
@@ -538,6 +566,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if constexpr (kStoreBufs == 2) ptx::bulk_wait_read<1>(); else ptx::bulk_wait_read<0>();
         }
         __syncwarp();
+        SS_PF(pe_prep);
         // gated accumulation: the 32 tokens of a chunk belong to one batch (rows_per_batch % 32 == 0)
         float gate[4] = {1.f, 1.f, 1.f, 1.f};
         if constexpr (GATED) {
@@ -582,8 +611,10 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                    packed[0], packed[1], packed[2], packed[3]);
           }
         }
+        SS_PF(pe_math);
         ptx::fence_proxy_async_smem();
         __syncwarp();
+        SS_PF(pe_fence);
         if (lane == 0) {
           // rows >= m and channels >= n are clipped by the tensor map; a box that lies wholly
           // beyond the last channel is not issued at all
@@ -600,8 +631,12 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
               ptx::tma_store_2d(dst, stage, ch_w, tok0 + c * 32);
             }
           }
+          SS_PF(pe_store);
           ptx::bulk_commit();
+          SS_PF(pe_commit);
+          SS_PF(pe_null);
         }
+        SS_PF(pe_reconv);
         ++store_it;
       };
       const int mine = chunks > half ? (chunks - half + kPairSub - 1) / kPairSub : 0;
@@ -614,16 +649,41 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int i = 0; i < kMine; ++i) {
           if (i < mine) {
             const int c = half + kPairSub * i;
+            SS_PF(pe_rest);
             ptx::tc_wait_ld();
-            if (i + 1 < mine) load(f[(i + 1) & 1], c + kPairSub); else release();
+            // The accumulator goes back to the MMA thread as soon as its last chunk is in registers:
+            // when the load issued here is the last one it is waited for at once (its latency, some
+            // 80 cycles, is then not hidden behind an emit) and the buffer is released a whole emit
+            // earlier.  With few stages per tile the MMA thread otherwise waits for this release.
+            if (i + 1 < mine) load(f[(i + 1) & 1], c + kPairSub);
+            if (i + 2 == mine) { ptx::tc_wait_ld(); release(); }
+            else if (mine == 1) release();
+            SS_PF(pe_ld);
             if (!(args.debug & 8)) emit(f[i & 1], c, sa_mine[i]);
+#ifdef SS_TIMELINE
+            ++pe_chunks;
+#endif
           }
         }
       }
       if (tl_warp) SS_TL(2, tl, 3);
+#ifdef SS_TIMELINE
+      if (tl_warp && tl == 0) {        // the first tile's sums on their own
+        SS_PF_STORE(32, pe_acc); SS_PF_STORE(33, pe_ld); SS_PF_STORE(34, pe_prep); SS_PF_STORE(35, pe_math);
+        SS_PF_STORE(36, pe_fence); SS_PF_STORE(37, pe_store); SS_PF_STORE(38, pe_rest); SS_PF_STORE(39, pe_chunks);
+        SS_PF_STORE(40, pe_commit); SS_PF_STORE(41, pe_reconv);
+      }
+#endif
     }
     if (lane == 0) ptx::bulk_wait_all();
     __syncwarp();
+#ifdef SS_TIMELINE
+    if (tl_warp) {
+      SS_PF_STORE(16, pe_acc); SS_PF_STORE(17, pe_ld); SS_PF_STORE(18, pe_prep); SS_PF_STORE(19, pe_math);
+      SS_PF_STORE(20, pe_fence); SS_PF_STORE(21, pe_store); SS_PF_STORE(22, pe_rest); SS_PF_STORE(23, pe_chunks);
+      SS_PF_STORE(24, pe_commit); SS_PF_STORE(25, pe_null); SS_PF_STORE(26, pe_reconv);
+    }
+#endif
     if (!ok && lane == 0) atomicOr(args.status, kStatusEpilogueTimeout);
   } else {
     // ------------------------------------------------------------------ epilogue, direct stores
@@ -636,39 +696,36 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     // tile is processed): lane l holds the scale of token l of each of the warp's chunks.
     constexpr int kMine = (T::kChunks + kPairSub - 1) / kPairSub;
     float sa_next[kMine], sw_next = 1.f, bias_next = 0.f;
-    auto prefetch = [&](int t) {
-      const int pch = (t % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
-      const int ptok0 = (t / tiles_ch2) * NT;
+    // indices clamped into range rather than loads under a condition: see the TMA-store epilogue
+    const int last_tok = args.m - 1, last_ch = args.n - 1;
+    TileWalk nxt(tile_first, tile_step, tiles_ch2);
+    auto prefetch = [&]() {
+      const int pch = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
+      const int ptok = nxt.tok * NT + half * 32 + lane;
 #pragma unroll
-      for (int i = 0; i < kMine; ++i) {
-        const int in_tile = (half + kPairSub * i) * 32 + lane;
-        sa_next[i] = (in_tile < NT && ptok0 + in_tile < args.m) ? __ldg(args.sa + ptok0 + in_tile) : 1.f;
-      }
-      sw_next = 1.f;
-      bias_next = 0.f;
-      if (pch < args.n) {
-        sw_next = __ldg(args.sw + pch);
-        if (args.bias) bias_next = __ldg(args.bias + pch);
-      }
+      for (int i = 0; i < kMine; ++i) sa_next[i] = __ldg(args.sa + min(ptok + kPairSub * 32 * i, last_tok));
+      sw_next = __ldg(args.sw + min(pch, last_ch));
+      if (args.bias) bias_next = __ldg(args.bias + min(pch, last_ch));
     };
     ptx::grid_dep_wait();
     if constexpr (!INT32_OUT) {
-      if (tile_first < num_tiles) prefetch(tile_first);
+      if (nxt.tile < num_tiles) prefetch();
     }
-    for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++acc_it) {
+    for (; nxt.tile < num_tiles && ok; ++acc_it) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
-      const int ch = (tile % tiles_ch2) * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
-      const int tok0 = (tile / tiles_ch2) * NT;
+      const int ch = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
+      const int tok0 = nxt.tok * NT;
       const bool ch_ok = ch < args.n;
       float sa_mine[kMine], sw = 1.f, bias = 0.f;
 #pragma unroll
       for (int i = 0; i < kMine; ++i) sa_mine[i] = 1.f;
+      nxt.advance();
       if constexpr (!INT32_OUT) {
 #pragma unroll
         for (int i = 0; i < kMine; ++i) sa_mine[i] = sa_next[i];
         sw = sw_next;
         bias = bias_next;
-        if (tile + tile_step < num_tiles) prefetch(tile + tile_step);
+        if (nxt.tile < num_tiles) prefetch();
       }
       int chunks = (args.m - tok0 + 31) / 32;
       chunks = chunks < T::kChunks ? chunks : T::kChunks;
@@ -696,7 +753,11 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if (i < mine) {
             const int c = half + kPairSub * i;
             ptx::tc_wait_ld();
-            if (i + 1 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + kPairSub) * 32, r[(i + 1) & 1]); else release();
+            // as in the TMA-store epilogue: the last load is waited for where it is issued, so that
+            // the accumulator is released before the last two chunks are stored
+            if (i + 1 < mine) ptx::tc_ld_32x32b_x32(t_addr + (c + kPairSub) * 32, r[(i + 1) & 1]);
+            if (i + 2 == mine) { ptx::tc_wait_ld(); release(); }
+            else if (mine == 1) release();
             store_chunk<INT32_OUT, HAS_ADDEND>(r[i & 1], args, sa_mine[i], tok0 + c * 32, tok_end, ch, ch_ok, sw, bias);
           }
         }
