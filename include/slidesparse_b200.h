@@ -298,18 +298,23 @@ int ss_gemm_resources(int64_t m, int64_t n, int64_t pk, int64_t* out, int n_out)
 /* Synchronises `stream`, writes the device status word of the current device to *status and
  * clears it.  0 = no kernel gave up on a bounded wait since the last read: returns SS_OK.
  * Otherwise returns SS_E_DEVICE (bits: 1 TMA producer, 2 MMA issuer, 4 epilogue, 8 wait-limit
- * probe); outputs of the launches since the previous check are then not to be trusted. */
+ * probe); outputs of the launches since the previous check are then not to be trusted (the call
+ * also clears the sums a split-schedule launch may have left half done). */
 int ss_device_status(void* stream, int32_t* status);
 
 /* ---- tuning switches ----------------------------------------------------------------------- */
 
 /* The library reads its switches from the environment once, at first use (SS_TOKEN_TILE,
- * SS_WIDE_CP, SS_META_WARP, SS_STORE, SS_RESIDENT, SS_PDL, SS_WAIT_NS); these two entries read and
+ * SS_WIDE_CP, SS_META_WARP, SS_STORE, SS_RESIDENT, SS_PDL, SS_SPLIT, SS_WAIT_NS); these two entries read and
  * change them afterwards, for tests and measurements.  No counterpart in the reference.  Names:
  * "token_tile" (0 = automatic, or 128/192/224/240/256), "wide_cp", "meta_warp" (-1 = automatic),
  * "store" (1 = TMA-store epilogue), "resident" (weights-resident form), "pdl" (programmatic
- * dependent launch), "wait_ns" (limit of every device-side wait, default 2e9).  Not synchronised
- * with concurrent launches from other threads. */
+ * dependent launch), "split" (schedule of the GEMM in which the clusters share the tiles x stages
+ * evenly and a tile computed by several clusters is summed through device memory the library
+ * allocates on the first such launch, 19 MB: -1 = where the cost model prefers it, 0 never,
+ * 1 wherever the output form allows; the results are the same bits either way), "wait_ns" (limit
+ * of every device-side wait, default 2e9).  Not synchronised with concurrent launches from other
+ * threads. */
 int ss_set_option(const char* name, int64_t value);
 int ss_get_option(const char* name, int64_t* value);
 

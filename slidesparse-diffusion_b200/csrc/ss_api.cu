@@ -293,7 +293,11 @@ extern "C" int ss_device_status(void* stream, int32_t* status) {
   SS_REQUIRE(p, SS_E_CUDA, "device status word unavailable");
   uint32_t v = 0;
   SS_CUDA(cudaMemcpy(&v, p, sizeof(v), cudaMemcpyDeviceToHost));
-  if (v) SS_CUDA(cudaMemset(p, 0, sizeof(v)));
+  if (v) {
+    SS_CUDA(cudaMemset(p, 0, sizeof(v)));
+    // a launch that gave up may have left sums of shared tiles behind
+    if (int rc = reset_split_workspace()) return rc;
+  }
   *status = static_cast<int32_t>(v);
   SS_REQUIRE(v == 0, SS_E_DEVICE,
              "a kernel gave up on a bounded wait (status 0x%x:%s%s%s%s); results of the launches since the "
@@ -308,6 +312,7 @@ struct OptionField { const char* name; int Options::*field; };
 const OptionField kOptionFields[] = {
     {"token_tile", &Options::token_tile}, {"wide_cp", &Options::wide_cp}, {"meta_warp", &Options::meta_warp},
     {"store", &Options::store},           {"resident", &Options::resident}, {"pdl", &Options::pdl},
+    {"split", &Options::split},
 };
 }  // namespace
 

@@ -50,6 +50,7 @@ struct Options {
   int store = 1;          // 1 = TMA-store epilogue where alignment allows, 0 = direct stores
   int resident = 1;       // weights-resident form where applicable
   int pdl = 1;            // programmatic dependent launch between front-end and GEMM
+  int split = -1;         // split schedule of the GEMM: -1 = where the cost model prefers it, 0 never, 1 wherever eligible
   unsigned long long wait_ns = kDefaultWaitNs;
 };
 Options& options();
@@ -108,12 +109,17 @@ struct GemmArgs {
   unsigned long long wait_ns = 0;
   int debug = 0;
   unsigned long long* probe = nullptr;
+  // false: the launch may not use the library's own device memory beyond the status word (the
+  // split schedule sums shared tiles in an area the library allocates on first use)
+  bool allow_split = true;
 };
 constexpr int kMaxPeers = 8;
 struct GemmResources {
   int threads, smem, regs, local, ctas_per_sm, token_tile, stages, tmem_cols;
 };
 int launch_gemm(const GemmArgs& a, cudaStream_t stream);
+// Zeroes the split schedule's tile-sum area of the current device (after a launch that gave up on a wait).
+int reset_split_workspace();
 int gemm_resources(int64_t m, int64_t n, int64_t pk, GemmResources* r);
 
 }  // namespace ss

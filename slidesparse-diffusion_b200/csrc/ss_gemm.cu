@@ -52,6 +52,8 @@ struct KernelArgs {
   unsigned long long wait_ns;      // limit of every mbarrier wait
   int debug;                       // diagnostics: bit 0 no MMAs, 1 no epilogue work, 2 no TMA stores, 3 TMEM loads only
   unsigned long long* probe;       // diagnostics: cluster 0 writes {cycles of its tile loop, stages}
+  int32_t* split_sum;              // split schedule: the clusters' slabs for pieces of shared tiles
+  int* split_ticket;               // split schedule: arrivals per epilogue warp of a shared tile (zero between launches)
 };
 
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes,
@@ -130,10 +132,17 @@ struct MapKeyEq {
 constexpr size_t kMapCacheLimit = 8192;   // descriptors kept; the cache starts over beyond this
 
 // kernel variants: token tile x output mode x resident form
-constexpr int kTileCount = 5, kModeCount = 6;
+constexpr int kTileCount = 5, kModeCount = 7;
 struct DeviceInfo {
   int sms = 0;
   std::atomic<bool> configured[kTileCount][kModeCount][2];
+  // split schedule: one slab of tile sums per cluster and one ticket per epilogue warp, allocated on
+  // the first launch that wants them (never during a stream capture) and zero between launches
+  std::mutex split_mu;
+  std::atomic<bool> split_ready{false};
+  int32_t* split_sum = nullptr;
+  int* split_ticket = nullptr;
+  size_t split_bytes = 0;
   DeviceInfo() { for (auto& a : configured) for (auto& b : a) for (auto& c : b) c.store(false); }
 };
 DeviceInfo* device_info() {
@@ -159,28 +168,81 @@ DeviceInfo* device_info() {
 // configurations (K' 1152 .. 18432, M 256 .. 16384).  The per-tile part is the pipeline fill, the
 // epilogue tail and the barrier round trips; 256 has a single accumulator, so its epilogue is
 // exposed.  Over those shapes the model's choice costs 0.4 % more than the best tile per shape.
+// The split schedule's area exists (or can be made to exist now: not while `stream` is capturing).
+bool split_workspace(DeviceInfo* dev, cudaStream_t stream) {
+  if (dev->split_ready.load(std::memory_order_acquire)) return true;
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return false;
+  }
+  std::lock_guard<std::mutex> lock(dev->split_mu);
+  if (dev->split_ready.load(std::memory_order_acquire)) return true;
+  const size_t clusters = static_cast<size_t>(dev->sms / 2);
+  const size_t sum_bytes = clusters * 2 * static_cast<size_t>(kSplitClusterWords) * sizeof(int32_t);   // two slabs per cluster
+  const size_t ticket_bytes = clusters * 2 * kPairEpiWarps * sizeof(int);
+  void* p = nullptr;
+  if (cudaMalloc(&p, sum_bytes + ticket_bytes) != cudaSuccess || cudaMemset(p, 0, sum_bytes + ticket_bytes) != cudaSuccess ||
+      cudaDeviceSynchronize() != cudaSuccess) {
+    cudaGetLastError();
+    if (p) cudaFree(p);
+    return false;
+  }
+  dev->split_sum = static_cast<int32_t*>(p);
+  dev->split_ticket = reinterpret_cast<int*>(static_cast<char*>(p) + sum_bytes);
+  dev->split_bytes = sum_bytes + ticket_bytes;
+  dev->split_ready.store(true, std::memory_order_release);
+  return true;
+}
+
 constexpr int kTiles[kTileCount] = {128, 192, 224, 240, 256};
 constexpr double kPerBlock[kTileCount] = {351.0, 415.0, 414.0, 425.0, 448.0};
 constexpr double kPerTile[kTileCount] = {2477.0, 2813.0, 4107.0, 3925.0, 5799.0};
 
-int pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms, bool whole_chunks_only) {
+// Split schedule (see Walk in ss_gemm_pair.cuh): the clusters share the tiles x stages evenly, so a
+// launch costs tiles / clusters (not rounded up) tile costs, plus what the shared tiles cost: every
+// cluster stores one accumulator to global memory at the start of its range and fetches one at the
+// end, where nothing hides it, and the clusters no longer walk K in step (measured over 20 shapes:
+// 5-6 us, of which the last piece's fetch and epilogue are about 2 us).  It therefore pays only when
+// a whole-tile launch would idle most clusters through a long last round, e.g. 2048 x 9728 -> 2432
+// (4:6): 100 tiles of 76 stages on 74 clusters, 42.7 -> 38.3 us.
+constexpr double kSplitExtra = 11000.0;
+
+struct TilePick { int nt; double cost; };
+TilePick pick_pair_token_tile(int64_t m, int64_t pn, int64_t pk, int sms, bool whole_chunks_only, bool split = false) {
   const int forced = options().token_tile;
-  for (int i = 0; i < kTileCount; ++i)
-    if (forced == kTiles[i] && !(whole_chunks_only && forced % 32)) return forced;
   const int64_t tiles_ch2 = (pn + 2 * kTileCh - 1) / (2 * kTileCh);
   const double num_kb = static_cast<double>(pk / kBlockK);
   const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
-  double best = 0;
-  int best_nt = 224;
+  TilePick best{224, 0};
   for (int i = 0; i < kTileCount; ++i) {
     const int nt = kTiles[i];
     if (whole_chunks_only && nt % 32) continue;
+    if (forced && forced != nt) continue;
     const int64_t tiles = tiles_ch2 * ((m + nt - 1) / nt);
-    const int64_t rounds = (tiles + pairs - 1) / pairs;
-    const double cost = static_cast<double>(rounds) * (num_kb * kPerBlock[i] + kPerTile[i]);
-    if (best == 0 || cost < best * 0.999) { best = cost; best_nt = nt; }
+    const double per_tile = num_kb * kPerBlock[i] + kPerTile[i];
+    double cost;
+    if (split) {
+      // with fewer tiles than clusters a tile is shared by many and its last piece adds up many
+      // slabs: measured slower than the whole-tile schedule throughout, unless forced
+      if (tiles < pairs && options().split != 1) continue;
+      const double rounds = static_cast<double>(tiles) / static_cast<double>(pairs);
+      cost = (rounds < 1.0 ? num_kb * kPerBlock[i] * rounds + kPerTile[i] : rounds * per_tile) + kSplitExtra;
+    } else {
+      cost = static_cast<double>((tiles + pairs - 1) / pairs) * per_tile;
+    }
+    if (best.cost == 0 || cost < best.cost * 0.999) best = {nt, cost};
   }
-  return best_nt;
+  if (best.cost == 0 && !split) {          // a forced tile the form excludes (the half chunk of 240): as if none were forced
+    for (int i = 0; i < kTileCount; ++i) {
+      const int nt = kTiles[i];
+      if (whole_chunks_only && nt % 32) continue;
+      const int64_t tiles = tiles_ch2 * ((m + nt - 1) / nt);
+      const double cost = static_cast<double>((tiles + pairs - 1) / pairs) * (num_kb * kPerBlock[i] + kPerTile[i]);
+      if (best.cost == 0 || cost < best.cost * 0.999) best = {nt, cost};
+    }
+  }
+  return best;
 }
 
 // ---- launcher ----------------------------------------------------------------------------------
@@ -247,10 +309,18 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int tile_index, cudaStream
   k.wait_ns = a.wait_ns ? a.wait_ns : opt.wait_ns;
   k.debug = a.debug;
   k.probe = a.probe;
+  k.split_sum = dev->split_sum;
+  k.split_ticket = dev->split_ticket;
   const int64_t tiles_ch2 = (k.tiles_ch + 1) / 2;
   const int64_t tiles = tiles_ch2 * k.tiles_tok;
   const int64_t pairs = dev->sms / 2;
   unsigned grid = 2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs);
+  if constexpr (MODE == kOutBf16TmaSplit) {
+    // every cluster takes an equal share of the tiles x stages
+    SS_REQUIRE(k.split_sum && k.split_ticket, SS_E_ARG, "gemm: the split schedule has no tile-sum area");
+    const int64_t units = tiles * ((k.num_kb + KB - 1) / KB);
+    grid = 2u * static_cast<unsigned>(units < pairs ? units : pairs);
+  }
   int smem_bytes = T::kSmemBytes;
   if constexpr (RES) {
     // a whole number of clusters per channel tile, so that a cluster never changes its weights
@@ -262,7 +332,7 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int tile_index, cudaStream
   }
   map_out = map_a;         // unused by the direct-store epilogues
   map_out_tail = map_a;
-  if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) {
+  if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd || MODE == kOutBf16TmaSplit) {
     // out[m, n] BF16, row pitch out_stride: one 32-channel x 32-token box per epilogue warp and chunk;
     // the epilogue writes its 64-byte rows with the 16-byte pieces XOR-swizzled (bank-conflict-free stmatrix)
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(a.n), static_cast<cuuint64_t>(a.m)};
@@ -336,7 +406,8 @@ bool tma_store_ok(const GemmArgs& a) {
 }
 
 template <int NT, int KB>
-int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int tile_index, cudaStream_t stream, int res_stages = 0) {
+int launch_pair_nt(const GemmArgs& a, DeviceInfo* dev, int tile_index, cudaStream_t stream, int res_stages = 0, bool split = false) {
+  if (split) return launch_pair_t<NT, KB, kOutBf16TmaSplit>(a, dev, tile_index, stream);
   if (a.int32_out) return launch_pair_t<NT, KB, kOutInt32>(a, dev, tile_index, stream);
   if (a.addend) return launch_pair_t<NT, KB, kOutBf16Addend>(a, dev, tile_index, stream);
   const bool aligned = tma_store_ok(a);
@@ -391,20 +462,28 @@ int check_args(const GemmArgs& a) {
 
 // The tile and form launch_gemm uses for a problem: token tile, resident pipeline depth (0 = the
 // streaming form).
-struct Choice { int nt; int res_stages; };
-Choice choose(const GemmArgs& a, int sms) {
+struct Choice { int nt; int res_stages; bool split; };
+Choice choose(const GemmArgs& a, int sms, bool split_allowed) {
   const Options& opt = options();
   if (opt.resident && !a.int32_out && !a.addend && a.peer_count == 0 && opt.token_tile == 0 && tma_store_ok(a)) {
     // prefer the token tile that needs fewer rounds of the clusters that share a channel tile
     const int s224 = resident_stages<224>(a, sms), s192 = resident_stages<192>(a, sms);
     const int64_t tiles_ch2 = (a.pn + 2 * kTileCh - 1) / (2 * kTileCh), group = (sms / 2) / (tiles_ch2 ? tiles_ch2 : 1);
     auto rounds = [&](int nt) { const int64_t t = (a.m + nt - 1) / nt; return (t + group - 1) / group; };
-    if (s224 && (!s192 || rounds(224) * 224 <= rounds(192) * 192)) return {224, s224};
-    if (s192) return {192, s192};
+    if (s224 && (!s192 || rounds(224) * 224 <= rounds(192) * 192)) return {224, s224, false};
+    if (s192) return {192, s192, false};
   }
   // the half chunk of the 240-token tile exists in the TMA-store epilogues only
   const bool whole_chunks_only = a.peer_count > 0;
-  return {pick_pair_token_tile(a.m, a.pn, a.pk, sms, whole_chunks_only), 0};
+  const TilePick whole = pick_pair_token_tile(a.m, a.pn, a.pk, sms, whole_chunks_only);
+  // the split schedule: plain aligned BF16 output only, at least two stages per tile, and worth its
+  // extra trip through global memory by the cost model (or forced)
+  if (split_allowed && opt.split != 0 && a.allow_split && opt.store == 1 && !a.int32_out && !a.addend && !a.gate &&
+      a.peer_count == 0 && tma_store_ok(a) && a.pk / kBlockK >= 4) {
+    const TilePick shared = pick_pair_token_tile(a.m, a.pn, a.pk, sms, false, true);
+    if (shared.cost > 0 && (opt.split == 1 || shared.cost < 0.93 * whole.cost)) return {shared.nt, 0, true};
+  }
+  return {whole.nt, 0, false};
 }
 
 }  // namespace
@@ -422,6 +501,7 @@ Options& options() {
     o->store = read("SS_STORE", 1);
     o->resident = read("SS_RESIDENT", 1);
     o->pdl = read("SS_PDL", 1);
+    o->split = read("SS_SPLIT", -1);
     if (const char* env = std::getenv("SS_WAIT_NS")) {
       const long long v = std::atoll(env);
       if (v > 0) o->wait_ns = static_cast<unsigned long long>(v);
@@ -469,18 +549,30 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   if (int rc = check_args(a)) return rc;
   DeviceInfo* dev = device_info();
   SS_REQUIRE(dev, SS_E_CUDA, "gemm: no current CUDA device");
-  const Choice c = choose(a, dev->sms);
+  Choice c = choose(a, dev->sms, true);
+  // the tile-sum area is made on the first launch that wants it; a launch that cannot have it (a
+  // stream capture before any such launch, no memory) takes the whole-tile schedule
+  if (c.split && !split_workspace(dev, stream)) c = choose(a, dev->sms, false);
   switch (c.nt) {
-    case 128: return launch_pair_nt<128, 2>(a, dev, 0, stream);
-    case 192: return launch_pair_nt<192, 2>(a, dev, 1, stream, c.res_stages);
-    case 224: return launch_pair_nt<224, 2>(a, dev, 2, stream, c.res_stages);
-    case 240: return launch_pair_nt<240, 2>(a, dev, 3, stream);
-    default:  return launch_pair_nt<256, 2>(a, dev, 4, stream);
+    case 128: return launch_pair_nt<128, 2>(a, dev, 0, stream, 0, c.split);
+    case 192: return launch_pair_nt<192, 2>(a, dev, 1, stream, c.res_stages, c.split);
+    case 224: return launch_pair_nt<224, 2>(a, dev, 2, stream, c.res_stages, c.split);
+    case 240: return launch_pair_nt<240, 2>(a, dev, 3, stream, 0, c.split);
+    default:  return launch_pair_nt<256, 2>(a, dev, 4, stream, 0, c.split);
   }
 }
 
+int reset_split_workspace() {
+  DeviceInfo* dev = device_info();
+  SS_REQUIRE(dev, SS_E_CUDA, "no current CUDA device");
+  if (!dev->split_ready.load(std::memory_order_acquire)) return SS_OK;
+  SS_CUDA(cudaMemset(dev->split_sum, 0, dev->split_bytes));
+  SS_CUDA(cudaDeviceSynchronize());
+  return SS_OK;
+}
+
 template <int NT, int KB>
-static int pair_resources_t(GemmResources* r, int res_stages, int slabs) {
+static int pair_resources_t(GemmResources* r, int res_stages, int slabs, bool split = false) {
   using T = PairTile<NT, KB>;
   cudaFuncAttributes attr;
   int smem = T::kSmemBytes, stages = T::kStages;
@@ -497,9 +589,15 @@ static int pair_resources_t(GemmResources* r, int res_stages, int slabs) {
       return SS_OK;
     }
   }
-  auto kernel = sparse_gemm_pair_kernel<NT, KB, kOutBf16Tma>;
-  SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
-  SS_CUDA(cudaFuncGetAttributes(&attr, kernel));
+  if (split) {
+    auto kernel = sparse_gemm_pair_kernel<NT, KB, kOutBf16TmaSplit>;
+    SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
+    SS_CUDA(cudaFuncGetAttributes(&attr, kernel));
+  } else {
+    auto kernel = sparse_gemm_pair_kernel<NT, KB, kOutBf16Tma>;
+    SS_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes));
+    SS_CUDA(cudaFuncGetAttributes(&attr, kernel));
+  }
   r->threads = kPairThreads; r->smem = smem; r->regs = attr.numRegs;
   r->local = static_cast<int>(attr.localSizeBytes); r->ctas_per_sm = 1;
   r->token_tile = NT; r->stages = stages; r->tmem_cols = kTmemCols;
@@ -513,14 +611,14 @@ int gemm_resources(int64_t m, int64_t n, int64_t pk, GemmResources* r) {
   GemmArgs a{};
   a.m = m; a.n = n; a.pm = ceil_to(m, 32); a.pn = ceil_to(n, 32); a.pk = pk;
   a.out = nullptr; a.out_stride = ceil_to(n, 8);
-  const Choice c = choose(a, dev->sms);
+  const Choice c = choose(a, dev->sms, true);
   const int slabs = static_cast<int>((pk / kBlockK + 1) / 2);
   switch (c.nt) {
-    case 128: return pair_resources_t<128, 2>(r, 0, slabs);
-    case 192: return pair_resources_t<192, 2>(r, c.res_stages, slabs);
-    case 224: return pair_resources_t<224, 2>(r, c.res_stages, slabs);
-    case 240: return pair_resources_t<240, 2>(r, 0, slabs);
-    default:  return pair_resources_t<256, 2>(r, 0, slabs);
+    case 128: return pair_resources_t<128, 2>(r, 0, slabs, c.split);
+    case 192: return pair_resources_t<192, 2>(r, c.res_stages, slabs, c.split);
+    case 224: return pair_resources_t<224, 2>(r, c.res_stages, slabs, c.split);
+    case 240: return pair_resources_t<240, 2>(r, 0, slabs, c.split);
+    default:  return pair_resources_t<256, 2>(r, 0, slabs, c.split);
   }
 }
 

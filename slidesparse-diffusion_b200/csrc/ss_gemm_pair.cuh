@@ -54,21 +54,57 @@ __device__ long long g_profile[kTlClusters * kPfSlots];
 #define SS_PF_STORE(slot, value) do {} while (0)
 #endif
 
-// A cluster's position in its tile sequence (tile = token tile * tiles_ch2 + channel tile, advancing
-// by the cluster count), kept as the two tile indices so that no role divides once per tile: an
-// integer division by a run-time value is a chain of some 40 dependent instructions.
-struct TileWalk {
-  int tile, ch, tok;
-  int step, step_ch, step_tok, tiles_ch2;
-  __device__ __forceinline__ TileWalk(int first, int step_, int tiles_ch2_)
-      : tile(first), ch(first % tiles_ch2_), tok(first / tiles_ch2_),
-        step(step_), step_ch(step_ % tiles_ch2_), step_tok(step_ / tiles_ch2_), tiles_ch2(tiles_ch2_) {}
-  __device__ __forceinline__ void advance() {
-    tile += step;
-    ch += step_ch;
-    tok += step_tok;
-    if (ch >= tiles_ch2) { ch -= tiles_ch2; ++tok; }
+// The pieces of work of a cluster, in order; a piece is the stages [s0, s1) of one tile (channel
+// tile ch, token tile tok; tile = tok * tiles_ch2 + ch).
+//   Whole-tile schedule: tiles pair, pair + clusters, ..., each with all its stages.  The two tile
+//   indices are advanced without a division per tile (an integer division by a run-time value is a
+//   chain of some 40 dependent instructions).
+//   Split schedule (SPLIT): the launch's tiles x stages, in tile order, are cut into one contiguous
+//   range per cluster, all of the same length to within one stage, so that no cluster idles in a
+//   last partial round; a tile whose K extent is shared by several clusters is summed through
+//   global memory (see the epilogue).
+template <bool SPLIT>
+struct Walk {
+  int tile, ch, tok, s0, s1;
+  bool valid;
+  int step, step_ch, step_tok, tiles_ch2, num_st;
+  long long pos, hi;
+  __device__ __forceinline__ Walk(int pair, int num_pairs, int tiles_ch2_, int num_tiles, int num_st_)
+      : tiles_ch2(tiles_ch2_), num_st(num_st_) {
+    if constexpr (SPLIT) {
+      const long long total = static_cast<long long>(num_tiles) * num_st;
+      pos = pair * total / num_pairs;
+      hi = (pair + 1) * total / num_pairs;
+      step = step_ch = step_tok = 0;
+      valid = pos < hi;
+      decode();
+    } else {
+      tile = pair; ch = pair % tiles_ch2; tok = pair / tiles_ch2;
+      step = num_pairs; step_ch = num_pairs % tiles_ch2; step_tok = num_pairs / tiles_ch2;
+      s0 = 0; s1 = num_st; pos = 0; hi = num_tiles;
+      valid = tile < num_tiles;
+    }
   }
+  __device__ __forceinline__ void decode() {
+    tile = static_cast<int>(pos / num_st);
+    s0 = static_cast<int>(pos - static_cast<long long>(tile) * num_st);
+    const long long left = hi - pos;
+    s1 = s0 + left < num_st ? s0 + static_cast<int>(left) : num_st;
+    ch = tile % tiles_ch2;
+    tok = tile / tiles_ch2;
+  }
+  __device__ __forceinline__ void advance() {
+    if constexpr (SPLIT) {
+      pos += s1 - s0;
+      valid = pos < hi;
+      if (valid) decode();
+    } else {
+      tile += step; ch += step_ch; tok += step_tok;
+      if (ch >= tiles_ch2) { ch -= tiles_ch2; ++tok; }
+      valid = tile < static_cast<int>(hi);
+    }
+  }
+  __device__ __forceinline__ bool whole() const { return s0 == 0 && s1 == num_st; }
 };
 
 template <int NT, int KB>
@@ -117,10 +153,16 @@ enum : int {
   kOutBf16Tma = 3,     // BF16 staged in shared memory and written with TMA tiled stores
   kOutBf16GateAdd = 4, // as kOutBf16Tma, but out += bf16(gate[batch, channel] * y) by TMA reduction
   kOutBf16TmaPeers = 5, // as kOutBf16Tma, but every tile is stored to several destinations (peer GPUs)
+  kOutBf16TmaSplit = 6, // as kOutBf16Tma with the split schedule (see Walk): tiles may be shared by clusters
 };
 
 // Destination tensor maps of the tensor-parallel form; the other forms pass an empty struct.
 struct PeerMaps { CUtensorMap m[kMaxPeers]; };
+
+// Split schedule: words of the tile-sum area per epilogue warp (at most four 32 x 32 chunks) and
+// per cluster (two CTAs of kPairEpiWarps warps).
+constexpr int kSplitWarpWords = 4 * 1024;
+constexpr long long kSplitClusterWords = 2ll * kPairEpiWarps * kSplitWarpWords;
 struct NoPeers {};
 
 // Shared-memory layout of the weights-resident form (RES): the whole K extent of the CTA's 128
@@ -152,6 +194,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                         const __grid_constant__ Peers peers) {
   using T = PairTile<NT, KB>;
   constexpr bool INT32_OUT = MODE == kOutInt32, HAS_ADDEND = MODE == kOutBf16Addend;
+  constexpr bool SPLIT = MODE == kOutBf16TmaSplit;
+  static_assert(!(SPLIT && RES), "the split schedule streams its weights");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -192,7 +236,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   // Tile sequence of this cluster: pair, pair + num_pairs, ...; tile = token tile * tiles_ch2 +
   // channel tile.  The resident form is launched with a cluster count that is a multiple of
   // tiles_ch2, so every tile of a cluster has the same channel tile (tile % tiles_ch2).
-  const int tile_first = pair, tile_step = num_pairs;
+  const int tile_first = pair;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kBarStride; ++s) {
@@ -212,7 +256,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
     ptx::prefetch_tensormap(&map_e);
-    if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd) {
+    if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd || MODE == kOutBf16TmaSplit) {
       ptx::prefetch_tensormap(&map_out);
       if constexpr (T::kHalfTail) ptx::prefetch_tensormap(&map_out_tail);
     }
@@ -261,11 +305,11 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
       ptx::grid_dep_wait();           // q is written by the kernel launched just before this one
-      for (TileWalk w(tile_first, tile_step, tiles_ch2); w.tile < num_tiles && ok; w.advance(), ++tl) {
+      for (Walk<SPLIT> w(pair, num_pairs, tiles_ch2, num_tiles, num_st); w.valid && ok; w.advance(), ++tl) {
         const int ch0 = w.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh;
         const int tok0 = w.tok * NT + static_cast<int>(rank) * T::kHalf;
         SS_TL(0, tl, 0);
-        for (int st = 0; st < num_st; ++st) {
+        for (int st = w.s0; st < w.s1; ++st) {
           SS_PF_BEGIN();
           if (!ptx::mbar_wait(&bar_empty[s], phase ^ 1u, args.wait_ns)) { ok = false; break; }
           SS_PF(pf_wait);
@@ -338,8 +382,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t probe_stages = 0, last_buf = 0, last_use = 0, tl = 0;
       long long pf_acc = 0, pf_ready = 0, pf_mma = 0, pf_commit = 0, pf_peek = 0;
       (void)pf_acc; (void)pf_ready; (void)pf_mma; (void)pf_commit; (void)pf_peek;
-      int tile = tile_first;
-      bool more = tile < num_tiles;
+      Walk<SPLIT> w(pair, num_pairs, tiles_ch2, num_tiles, num_st);
+      bool more = w.valid;
       if constexpr (RES) {
         // once per cluster: metadata of the whole K extent from its staging area into TMEM
         if (more) {
@@ -358,7 +402,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
       if (probe) probe_begin = clock64();
-      int st = 0;
+      int st = w.s0, st_first = w.s0, st_end = w.s1;      // the current piece's stages
       uint32_t buf = 0, d_tmem = tmem_base;
       if (more && ok) {
         SS_TL(1, tl, 0);
@@ -376,7 +420,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             if (!meta_warp && !ptx::mbar_wait(&bar_e[slot], phase, args.wait_ns)) { ok = false; more = false; break; }
           }
           SS_PF(pf_ready);
-          if (st == 0) SS_TL(1, tl, 2);
+          if (st == st_first) SS_TL(1, tl, 2);
           ++probe_stages;
           ptx::tc_fence_after();
           // resident form: weights and metadata are indexed by the K position, not by the ring slot
@@ -398,7 +442,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           }
           // K = 64 lifted columns per instruction: 32 B of compressed weights, 64 B of activations per row
           if (issue_mma) {
-            ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo, kDescHiA), desc(b_lo, kDescHiB), e_tmem, idesc, st != 0 ? 1u : 0u);
+            ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo, kDescHiA), desc(b_lo, kDescHiB), e_tmem, idesc, st != st_first ? 1u : 0u);
             ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo + 2, kDescHiA), desc(b_lo + 4, kDescHiB), e_tmem + 2, idesc, 1u);
             if (KB == 2 && full_stage) {
               ptx::tc_mma_sp_i8_pair(d_tmem, desc(a_lo + 4, kDescHiA), desc(b_lo + (T::kBBlock >> 4), kDescHiB), e_tmem + 4, idesc, 1u);
@@ -414,18 +458,19 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           SS_PF(pf_commit);
           if (slot == kRing - 1) phase ^= 1u;
           SS_PF(pf_peek);
-          if (++st == num_st) {
-            // the tile is complete: publish the accumulator
+          if (++st == st_end) {
+            // the piece is complete: publish the accumulator
             ptx::tc_commit_pair(&bar_acc_full[buf], 3);
             SS_PF(pf_commit);
             SS_TL(1, tl, 3);
             last_buf = buf;
             last_use = acc_it / T::kAccBufs;
-            st = 0;
-            tile += tile_step;
+            w.advance();
             ++acc_it;
             ++tl;
-            if (tile >= num_tiles) { more = false; break; }
+            if (!w.valid) { more = false; break; }
+            st = st_first = w.s0;
+            st_end = w.s1;
             buf = acc_it % T::kAccBufs;
             d_tmem = tmem_base + buf * NT;
             SS_TL(1, tl, 0);
@@ -451,8 +496,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     if (meta_warp && lane == 0 && rank == 0) {
       uint32_t s = 0, phase = 0;
       bool ok = true;
-      for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step) {
-        for (int st = 0; st < num_st; ++st) {
+      for (Walk<SPLIT> w(pair, num_pairs, tiles_ch2, num_tiles, num_st); w.valid && ok; w.advance()) {
+        for (int st = w.s0; st < w.s1; ++st) {
           const int kb0 = st * KB;
           const int nkb = args.num_kb - kb0 < KB ? args.num_kb - kb0 : KB;
           // the stage's previous metadata is no longer read once its MMAs have completed, which
@@ -475,7 +520,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       if (!ok) atomicOr(args.status, kStatusMmaTimeout);
     }
-  } else if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd || MODE == kOutBf16TmaPeers) {
+  } else if constexpr (MODE == kOutBf16Tma || MODE == kOutBf16GateAdd || MODE == kOutBf16TmaPeers || MODE == kOutBf16TmaSplit) {
     // ------------------------------------------------------------------ epilogue, TMA stores
     constexpr bool GATED = MODE == kOutBf16GateAdd;
     // The accumulator is channel-major in TMEM (lane = channel, column = token) and the output is
@@ -503,7 +548,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
     for (int i = 0; i < 4; ++i) bias_next[i] = 0.f;
     const int last_tok = args.m - 1, last_ch = args.n - 1;
-    TileWalk nxt(tile_first, tile_step, tiles_ch2);
+    Walk<SPLIT> nxt(pair, num_pairs, tiles_ch2, num_tiles, num_st);
     auto prefetch = [&]() {
       const int pch = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane_ch;
       const int ptok = nxt.tok * NT + half * 32 + lane;
@@ -517,20 +562,78 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     };
     ptx::grid_dep_wait();             // sa is written by the kernel launched just before this one
-    if (nxt.tile < num_tiles) prefetch();
-    for (; nxt.tile < num_tiles && ok; ++acc_it, ++tl) {
+    if (nxt.valid) prefetch();
+    for (; nxt.valid && ok; ++acc_it, ++tl) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
       const int ch_w = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32;
       const int tok0 = nxt.tok * NT;
+      // Split schedule: a tile whose stages are shared by several clusters (`pieces` of them, the
+      // first being cluster `owner`) is completed through global memory: every piece but the last to
+      // arrive stores its accumulator in a slab of its own, and the last one adds them up and runs
+      // the epilogue (integer addition is exact, so the order of arrival does not matter, and nobody
+      // waits for anybody).  A cluster has two slabs: one for a piece that starts its tile (`head`:
+      // the last piece of the cluster's range) and one for a piece that does not (the first piece of
+      // its range).  Cluster c works on positions [c * total / clusters, (c + 1) * total / clusters)
+      // of the tiles x stages sequence, so position P belongs to cluster
+      // ceil((P + 1) * clusters / total) - 1.
+      bool partial = false, head = false;
+      int pieces = 1, owner = 0;
+      int* counter = nullptr;
+      if constexpr (SPLIT) {
+        partial = !nxt.whole();
+        if (partial) {
+          const long long total = static_cast<long long>(num_tiles) * num_st;
+          const long long first = static_cast<long long>(nxt.tile) * num_st;
+          owner = static_cast<int>(((first + 1) * num_pairs + total - 1) / total) - 1;
+          pieces = static_cast<int>(((first + num_st) * num_pairs + total - 1) / total) - owner;
+          head = nxt.s0 == 0;
+          counter = args.split_ticket + owner * (2 * kPairEpiWarps) + static_cast<int>(rank) * kPairEpiWarps + (warp - 2);
+        }
+      }
+      // this warp's part of a slab: chunk i, registers 4 g .. 4 g + 3 of lane l at uint4 (8 i + g) * 32 + l
+      auto slab = [&](int cluster, bool of_head) {
+        const long long slot = (static_cast<long long>(cluster) * 2 + (of_head ? 0 : 1)) * (2 * kPairEpiWarps) +
+                               static_cast<int>(rank) * kPairEpiWarps + (warp - 2);
+        return reinterpret_cast<uint4*>(args.split_sum) + slot * (kSplitWarpWords / 4) + lane;
+      };
       float sa_mine[kMine], sw[4], bias[4];
 #pragma unroll
       for (int i = 0; i < kMine; ++i) sa_mine[i] = sa_next[i];
 #pragma unroll
       for (int i = 0; i < 4; ++i) { sw[i] = sw_next[i]; bias[i] = bias_next[i]; }
       nxt.advance();
-      if (nxt.tile < num_tiles) prefetch();
+      if (nxt.valid) prefetch();
       int chunks = (args.m - tok0 + 31) / 32;
       chunks = chunks < T::kChunks ? chunks : T::kChunks;
+      const int mine = chunks > half ? (chunks - half + kPairSub - 1) / kPairSub : 0;
+      uint32_t f[2][32];
+      // split schedule: this warp's chunk i of a slab into registers
+      auto fetch = [&](uint32_t (&r)[32], const uint4* src, int i) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const uint4 v = __ldcg(src + (8 * i + g) * 32);
+          r[4 * g] = v.x; r[4 * g + 1] = v.y; r[4 * g + 2] = v.z; r[4 * g + 3] = v.w;
+        }
+      };
+      // are all the other pieces of the tile in?
+      auto others_in = [&]() {
+        int seen = 0;
+        if (lane == 0) seen = atomicAdd(counter, 0);
+        const bool all = __shfl_sync(0xffffffffu, seen, 0) == pieces - 1;
+        if (all) __threadfence();
+        return all;
+      };
+      // A head piece ends its cluster's range, the others start theirs, so the head piece is nearly
+      // always the last to arrive.  It looks while its own MMAs still run; if the others are all in
+      // it starts fetching the next cluster's slab now and later adds the slabs to its accumulator
+      // as that leaves TMEM, instead of storing and re-reading it.
+      bool finish = false, primed = false;
+      if constexpr (SPLIT) {
+        if (partial && head && mine > 0 && !(args.debug & 2)) {
+          finish = others_in();
+          if (finish) { fetch(f[1], slab(owner + 1, false), 0); primed = true; }
+        }
+      }
       if (tl_warp) SS_TL(2, tl, 0);
       SS_PF_BEGIN();
       if (!ptx::mbar_wait(&bar_acc_full[buf], acc_use & 1u, args.wait_ns)) { ok = false; break; }
@@ -639,11 +742,60 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         SS_PF(pe_reconv);
         ++store_it;
       };
-      const int mine = chunks > half ? (chunks - half + kPairSub - 1) / kPairSub : 0;
       if (mine == 0) {
         release();
+      } else if (SPLIT && partial) {
+        auto add_pieces = [&](int first_piece, int i) {       // f[0] += pieces first_piece .. of chunk i
+          for (int p = first_piece; p < pieces; ++p) {
+            fetch(f[1], slab(owner + p, p == 0), i);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[0][j] += f[1][j];
+          }
+        };
+        if (head && !finish) finish = others_in();
+        if (finish && !primed) fetch(f[1], slab(owner + 1, false), 0);
+        uint4* own = slab(pair, head);
+#pragma unroll
+        for (int i = 0; i < kMine; ++i) {
+          if (i < mine) {
+            const int c = half + kPairSub * i;
+            load(f[0], c);
+            ptx::tc_wait_ld();
+            if (i + 1 == mine) release();
+            if (finish) {
+              // the next cluster's slab (fetched during the previous chunk's emit), then any further ones
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[0][j] += f[1][j];
+              add_pieces(2, i);
+              if (i + 1 < mine) fetch(f[1], slab(owner + 1, false), i + 1);
+              emit(f[0], c, sa_mine[i]);
+            } else {
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                __stcg(own + (8 * i + g) * 32, make_uint4(f[0][4 * g], f[0][4 * g + 1], f[0][4 * g + 2], f[0][4 * g + 3]));
+            }
+          }
+        }
+        if (!finish) {
+          __threadfence();                  // this lane's stores before the ticket
+          __syncwarp();
+          int ticket = 0;
+          if (lane == 0) ticket = atomicAdd(counter, 1);
+          finish = __shfl_sync(0xffffffffu, ticket, 0) == pieces - 1;
+          if (finish) {
+            __threadfence();
+#pragma unroll
+            for (int i = 0; i < kMine; ++i) {
+              if (i < mine) {
+                fetch(f[0], slab(owner, true), i);
+                add_pieces(1, i);
+                emit(f[0], half + kPairSub * i, sa_mine[i]);
+              }
+            }
+          }
+        }
+        if (finish && lane == 0) atomicExch(counter, 0);      // zero between launches
       } else {
-        uint32_t f[2][32];
         load(f[0], half);
 #pragma unroll
         for (int i = 0; i < kMine; ++i) {
@@ -698,7 +850,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     float sa_next[kMine], sw_next = 1.f, bias_next = 0.f;
     // indices clamped into range rather than loads under a condition: see the TMA-store epilogue
     const int last_tok = args.m - 1, last_ch = args.n - 1;
-    TileWalk nxt(tile_first, tile_step, tiles_ch2);
+    Walk<false> nxt(pair, num_pairs, tiles_ch2, num_tiles, num_st);
     auto prefetch = [&]() {
       const int pch = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
       const int ptok = nxt.tok * NT + half * 32 + lane;
@@ -709,9 +861,9 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     };
     ptx::grid_dep_wait();
     if constexpr (!INT32_OUT) {
-      if (nxt.tile < num_tiles) prefetch();
+      if (nxt.valid) prefetch();
     }
-    for (; nxt.tile < num_tiles && ok; ++acc_it) {
+    for (; nxt.valid && ok; ++acc_it) {
       const uint32_t buf = acc_it % T::kAccBufs, acc_use = acc_it / T::kAccBufs;
       const int ch = nxt.ch * (2 * kTileCh) + static_cast<int>(rank) * kTileCh + quad * 32 + lane;
       const int tok0 = nxt.tok * NT;
@@ -725,7 +877,7 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int i = 0; i < kMine; ++i) sa_mine[i] = sa_next[i];
         sw = sw_next;
         bias = bias_next;
-        if (nxt.tile < num_tiles) prefetch();
+        if (nxt.valid) prefetch();
       }
       int chunks = (args.m - tok0 + 31) / 32;
       chunks = chunks < T::kChunks ? chunks : T::kChunks;

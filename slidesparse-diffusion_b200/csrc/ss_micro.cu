@@ -175,6 +175,7 @@ extern "C" int ss_micro_pair_rate(int64_t m, int64_t n, int64_t pk, int token_ti
              m, n, pm, pn, pk, false};
   a.debug = flags;
   a.probe = probe;
+  a.allow_split = false;          // the rate is that of the whole-tile schedule
   for (int rep = 0; rep < 3 && rc == SS_OK; ++rep) {          // the first launches warm up
     rc = launch_gemm(a, nullptr);
     if (rc == SS_OK && cudaDeviceSynchronize() != cudaSuccess) rc = SS_E_CUDA;

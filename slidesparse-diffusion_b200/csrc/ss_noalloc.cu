@@ -75,6 +75,7 @@ extern "C" int ss_projection_static(const void* x, int64_t sx, int64_t m, int64_
   auto s = static_cast<cudaStream_t>(stream);
   if (int rc = launch_quantize_lift(x, sx, m, k, group, q, sa, s)) return rc;
   GemmArgs a{q, packed, meta, sa, sw, bias, nullptr, 0, out, out_stride, m, n, pm, pn, pk, false};
-  a.overlap_prologue = true;      // same launch pair as ss_projection: the GEMM sets up under the front-end's tail
+  a.overlap_prologue = true;
+  a.allow_split = false;          // the split schedule's tile sums live in memory the library allocates      // same launch pair as ss_projection: the GEMM sets up under the front-end's tail
   return launch_gemm(a, s);
 }

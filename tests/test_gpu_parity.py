@@ -131,6 +131,61 @@ def test_large_token_tiles_full_height(backend, oracle, oracle_c, tile):
     assert backend.device_status() == 0
 
 
+@pytest.mark.parametrize("tile", [0, 128, 192, 224, 240, 256])
+@pytest.mark.parametrize("mode,m,k,n", [(6, 666, 2432, 2304), (8, 256, 3072, 1024), (4, 700, 1152, 5000), (6, 100, 9728, 304)])
+def test_split_schedule_is_exact(backend, oracle, oracle_c, tile, mode, m, k, n):
+    """The split schedule forced on (every cluster takes an equal share of the tiles x stages, shared
+    tiles are summed through global memory by whichever piece arrives last): the same bits as the
+    whole-tile schedule's oracle, launch after launch (the sums must be left zero), with tiles
+    shared by two and by many clusters, ragged M, N and K, and under CUDA-graph replay."""
+    case = prepare_case(oracle, m, k, n, mode, seed=tile + n)
+    expect = oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"])
+    q, packed, meta = dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32)
+    sa, sw, bias = dev(case["sa"]), dev(case["scales"]), dev(case["bias"])
+    pitch = -(-n // 8) * 8
+    lib = backend.library()
+    with option(backend, "split", 1), option(backend, "token_tile", tile), option(backend, "resident", 0):
+        for _ in range(3):
+            wide = torch.full((m, pitch + 8), float("nan"), dtype=torch.bfloat16, device=DEV)
+            check(backend, lib.ss_gemm_run(ptr(q), ptr(packed), ptr(meta), ptr(sa), ptr(sw), ptr(bias), None, 0, ptr(wide),
+                                           pitch + 8, m, n, q.shape[0], packed.shape[0], q.shape[1], stream()))
+            if n % 8 == 0:
+                assert np.array_equal(bits(wide[:, :n]), expect)
+                assert torch.isnan(wide[:, n:].float()).all()
+            else:
+                assert np.array_equal(bits(wide[:, :n]), expect)       # unaligned n: the direct-store form ran
+        if n % 8 == 0:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    check(backend, lib.ss_gemm_run(ptr(q), ptr(packed), ptr(meta), ptr(sa), ptr(sw), ptr(bias), None, 0, ptr(out),
+                                                   n, m, n, q.shape[0], packed.shape[0], q.shape[1], stream()))
+            torch.cuda.current_stream().wait_stream(side)
+            for _ in range(3):
+                out.fill_(float("nan"))
+                graph.replay()
+                torch.cuda.synchronize()
+                assert np.array_equal(bits(out), expect)
+    assert backend.device_status() == 0
+
+
+def test_split_schedule_chosen_by_the_cost_model(backend, oracle, oracle_c):
+    """A launch whose tiles fill a round and a fraction of the next (87 tiles of 224 tokens on 74
+    clusters): the library's own choice, against the split schedule switched off."""
+    m, k, n, mode = 666, 2432, 7296, 6
+    case = prepare_case(oracle, m, k, n, mode, seed=5)
+    expect = oracle_c.epilogue(case["acc"], case["sa"], case["scales"], case["bias"])
+    args = (dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32), dev(case["sa"]), dev(case["scales"]),
+            dev(case["bias"]), m, n)
+    assert np.array_equal(bits(c_gemm_run(backend, *args)), expect)
+    with option(backend, "split", 0):
+        assert np.array_equal(bits(c_gemm_run(backend, *args)), expect)
+    assert backend.device_status() == 0
+
+
 @pytest.mark.parametrize("mode,m,k,n", SHAPES)
 @pytest.mark.parametrize("with_bias", [True, False])
 def test_gemm_bf16_output(backend, oracle, oracle_c, mode, m, k, n, with_bias):
