@@ -298,8 +298,19 @@ def measure_shape(torch, sdk, oracle, device, label, mode, m, k, n, steps, warmu
     quantised = [sdk.quantize_lift(x, mode) for x in xs]
     timed = lambda fn: graph_time_us(torch, device, fn, copies, steps, warmup)
     full_us = timed(lambda: [op(x) for op, x in zip(ops, xs)])
-    gemm_us = timed(lambda: [torch.ops.sdacc_dualscale_sm80.run(q, op.packed, op.metadata, sa, op.scales, op.bias,
-                                                               m, n, 5, None) for op, (q, sa) in zip(ops, quantised)])
+    run_gemms = lambda: [torch.ops.sdacc_dualscale_sm80.run(q, op.packed, op.metadata, sa, op.scales, op.bias,
+                                                           m, n, 5, None) for op, (q, sa) in zip(ops, quantised)]
+    gemm_us = timed(run_gemms)
+    # the GEMM's two schedules (the library chooses per launch; "split" shares the tiles x stages evenly
+    # among the clusters): whole tiles only, and the split schedule wherever the output form allows
+    from slidesparse_diffusion_b200 import backend
+    schedule_us = {}
+    for name, value in (("whole_tiles", 0), ("split_forced", 1)):
+        backend.set_option("split", value)
+        try:
+            schedule_us[name] = timed(run_gemms)
+        finally:
+            backend.set_option("split", -1)
     front_us = timed(lambda: [torch.ops.sdacc_mild_projection_sm80.quantize(x, mode) for x in xs])
     dense_us = timed(lambda: [torch.nn.functional.linear(x, w, dense_b) for x, w in zip(xs, dense_w)])
     pm, pn = -(-m // 32) * 32, -(-n // 32) * 32
@@ -308,7 +319,8 @@ def measure_shape(torch, sdk, oracle, device, label, mode, m, k, n, steps, warmu
     t_hbm_us = gemm_bytes / pk["hbm_gbs"] / 1e3
     t_tensor_us = 2.0 * pm * pn * pkk / (4.0 * pk["bf16_tflops"]) / 1e6
     return {"shape": label, "mode": f"{mode - 2}:{mode}", "m": m, "k": k, "n": n, "copies": copies,
-            "projection_us": full_us, "gemm_us": gemm_us, "frontend_us": front_us, "dense_bf16_us": dense_us,
+            "projection_us": full_us, "gemm_us": gemm_us, "gemm_whole_tiles_us": schedule_us["whole_tiles"],
+            "gemm_split_forced_us": schedule_us["split_forced"], "frontend_us": front_us, "dense_bf16_us": dense_us,
             "logical_tops": 2.0 * m * n * k / full_us / 1e6,
             "gemm_executed_pct_of_9000": 100 * 2.0 * pm * pn * pkk / gemm_us / 1e6 / 9000.0,
             "gemm_algorithmic_bytes": gemm_bytes, "gemm_hbm_floor_us": t_hbm_us, "gemm_tensor_floor_us": t_tensor_us,
