@@ -311,10 +311,12 @@ int ss_device_status(void* stream, int32_t* status);
  * "store" (1 = TMA-store epilogue), "resident" (weights-resident form), "pdl" (programmatic
  * dependent launch), "split" (schedule of the GEMM in which the clusters share the tiles x stages
  * evenly and a tile computed by several clusters is summed through device memory the library
- * allocates on the first such launch, 19 MB: -1 = where the cost model prefers it, 0 never,
+ * allocates on the first such launch outside a stream capture, 152 MB (four areas of 38 MB, one per
+ * stream that launches this schedule; further streams keep whole tiles): -1 = where the cost model prefers it, 0 never,
  * 1 wherever the output form allows; the results are the same bits either way), "wait_ns" (limit
- * of every device-side wait, default 2e9).  Not synchronised with concurrent launches from other
- * threads. */
+ * of every device-side wait, default 2e9).  ss_get_option also answers "split_launches": how many
+ * GEMM launches of this process took the split schedule.  Not synchronised with concurrent
+ * launches from other threads. */
 int ss_set_option(const char* name, int64_t value);
 int ss_get_option(const char* name, int64_t* value);
 

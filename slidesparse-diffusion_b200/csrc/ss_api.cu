@@ -340,6 +340,10 @@ extern "C" int ss_get_option(const char* name, int64_t* value) {
     *value = static_cast<int64_t>(opt.wait_ns);
     return SS_OK;
   }
+  if (std::string(name) == "split_launches") {
+    *value = static_cast<int64_t>(split_launch_count());
+    return SS_OK;
+  }
   for (const OptionField& f : kOptionFields)
     if (std::string(name) == f.name) {
       *value = opt.*(f.field);

@@ -120,6 +120,8 @@ struct GemmResources {
 int launch_gemm(const GemmArgs& a, cudaStream_t stream);
 // Zeroes the split schedule's tile-sum area of the current device (after a launch that gave up on a wait).
 int reset_split_workspace();
+// GEMM launches of this process that took the split schedule (read-only "split_launches" of ss_get_option).
+long long split_launch_count();
 int gemm_resources(int64_t m, int64_t n, int64_t pk, GemmResources* r);
 
 }  // namespace ss

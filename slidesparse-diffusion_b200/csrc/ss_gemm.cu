@@ -136,13 +136,21 @@ constexpr int kTileCount = 5, kModeCount = 7;
 struct DeviceInfo {
   int sms = 0;
   std::atomic<bool> configured[kTileCount][kModeCount][2];
-  // split schedule: one slab of tile sums per cluster and one ticket per epilogue warp, allocated on
-  // the first launch that wants them (never during a stream capture) and zero between launches
+  // split schedule: two accumulator slabs per cluster and one ticket per epilogue warp (tickets zero
+  // between launches).  Launches on different streams may overlap, so each stream that launches the
+  // split schedule gets an area of its own out of a pool of kSplitAreas, allocated as a whole by the
+  // first such launch outside a stream capture (handing an area to a stream needs no CUDA call, so a
+  // capturing stream can still get one).  An area whose launches were all eager and have completed
+  // (an event recorded after each) goes to the next stream that asks; one used inside a capture stays
+  // with its stream, since the graph may be replayed at any time.  Streams that find no area, and
+  // captures before the pool exists, keep whole tiles.
+  static constexpr int kSplitAreas = 4;
+  struct SplitArea { cudaStream_t stream; int32_t* sum; int* ticket; cudaEvent_t done; bool pinned; bool used; int claims; };
   std::mutex split_mu;
-  std::atomic<bool> split_ready{false};
-  int32_t* split_sum = nullptr;
-  int* split_ticket = nullptr;
-  size_t split_bytes = 0;
+  SplitArea split_area[kSplitAreas] = {};
+  int split_areas = 0;            // areas handed to streams
+  void* split_pool = nullptr;
+  size_t split_bytes = 0;         // bytes of one area
   DeviceInfo() { for (auto& a : configured) for (auto& b : a) for (auto& c : b) c.store(false); }
 };
 DeviceInfo* device_info() {
@@ -168,31 +176,67 @@ DeviceInfo* device_info() {
 // configurations (K' 1152 .. 18432, M 256 .. 16384).  The per-tile part is the pipeline fill, the
 // epilogue tail and the barrier round trips; 256 has a single accumulator, so its epilogue is
 // exposed.  Over those shapes the model's choice costs 0.4 % more than the best tile per shape.
-// The split schedule's area exists (or can be made to exist now: not while `stream` is capturing).
-bool split_workspace(DeviceInfo* dev, cudaStream_t stream) {
-  if (dev->split_ready.load(std::memory_order_acquire)) return true;
-  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
-    cudaGetLastError();
-    return false;
-  }
+std::atomic<long long> g_split_launches{0};
+
+// The split schedule's area of `stream`, handed out now if `create` and one is left (the pool is
+// allocated here too, unless `stream` is capturing); nullptr if there is none.
+DeviceInfo::SplitArea* split_workspace(DeviceInfo* dev, cudaStream_t stream, bool create) {
   std::lock_guard<std::mutex> lock(dev->split_mu);
-  if (dev->split_ready.load(std::memory_order_acquire)) return true;
+  // `create` is the call of a launch that is about to use the area: it holds a claim on it until
+  // the launch has been issued (released in launch_gemm), so that no other thread's launch takes it
+  for (int i = 0; i < dev->split_areas; ++i)
+    if (dev->split_area[i].stream == stream) {
+      if (create) ++dev->split_area[i].claims;
+      return &dev->split_area[i];
+    }
+  if (!create) return nullptr;
+  if (dev->split_areas == DeviceInfo::kSplitAreas) {
+    for (DeviceInfo::SplitArea& area : dev->split_area) {
+      if (area.pinned || area.claims > 0 || (area.used && cudaEventQuery(area.done) != cudaSuccess)) continue;
+      area.stream = stream;          // its launches have completed: tickets are zero again
+      area.used = false;
+      area.claims = 1;
+      return &area;
+    }
+    cudaGetLastError();
+    return nullptr;
+  }
   const size_t clusters = static_cast<size_t>(dev->sms / 2);
   const size_t sum_bytes = clusters * 2 * static_cast<size_t>(kSplitClusterWords) * sizeof(int32_t);   // two slabs per cluster
-  const size_t ticket_bytes = clusters * 2 * kPairEpiWarps * sizeof(int);
-  void* p = nullptr;
-  if (cudaMalloc(&p, sum_bytes + ticket_bytes) != cudaSuccess || cudaMemset(p, 0, sum_bytes + ticket_bytes) != cudaSuccess ||
-      cudaDeviceSynchronize() != cudaSuccess) {
-    cudaGetLastError();
-    if (p) cudaFree(p);
-    return false;
+  const size_t ticket_bytes = (clusters * 2 * kPairEpiWarps * sizeof(int) + 255) / 256 * 256;
+  if (!dev->split_pool) {
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capture) != cudaSuccess || capture != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    const size_t total = (sum_bytes + ticket_bytes) * DeviceInfo::kSplitAreas;
+    void* p = nullptr;
+    if (cudaMalloc(&p, total) != cudaSuccess || cudaMemset(p, 0, total) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+      cudaGetLastError();
+      if (p) cudaFree(p);
+      return nullptr;
+    }
+    for (DeviceInfo::SplitArea& area : dev->split_area) {
+      if (cudaEventCreateWithFlags(&area.done, cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return nullptr;
+      }
+    }
+    dev->split_pool = p;
+    dev->split_bytes = sum_bytes + ticket_bytes;
   }
-  dev->split_sum = static_cast<int32_t*>(p);
-  dev->split_ticket = reinterpret_cast<int*>(static_cast<char*>(p) + sum_bytes);
-  dev->split_bytes = sum_bytes + ticket_bytes;
-  dev->split_ready.store(true, std::memory_order_release);
-  return true;
+  DeviceInfo::SplitArea& area = dev->split_area[dev->split_areas];
+  char* base = static_cast<char*>(dev->split_pool) + dev->split_bytes * dev->split_areas;
+  area.stream = stream;
+  area.sum = reinterpret_cast<int32_t*>(base);
+  area.ticket = reinterpret_cast<int*>(base + sum_bytes);
+  area.pinned = false;
+  area.used = false;
+  area.claims = 1;
+  ++dev->split_areas;
+  return &area;
 }
 
 constexpr int kTiles[kTileCount] = {128, 192, 224, 240, 256};
@@ -309,8 +353,17 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int tile_index, cudaStream
   k.wait_ns = a.wait_ns ? a.wait_ns : opt.wait_ns;
   k.debug = a.debug;
   k.probe = a.probe;
-  k.split_sum = dev->split_sum;
-  k.split_ticket = dev->split_ticket;
+  k.split_sum = nullptr;
+  k.split_ticket = nullptr;
+  DeviceInfo::SplitArea* split_area = nullptr;
+  if constexpr (MODE == kOutBf16TmaSplit) {
+    split_area = split_workspace(dev, stream, false);
+    if (split_area) {
+      k.split_sum = split_area->sum;
+      k.split_ticket = split_area->ticket;
+    }
+    g_split_launches.fetch_add(1, std::memory_order_relaxed);
+  }
   const int64_t tiles_ch2 = (k.tiles_ch + 1) / 2;
   const int64_t tiles = tiles_ch2 * k.tiles_tok;
   const int64_t pairs = dev->sms / 2;
@@ -374,6 +427,19 @@ int launch_pair_t(const GemmArgs& a, DeviceInfo* dev, int tile_index, cudaStream
   cfg.numAttrs = a.overlap_prologue && opt.pdl ? 1 : 0;
   SS_CUDA(cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_e, map_out, map_out_tail, k, peers));
   SS_CUDA(cudaGetLastError());
+  if (split_area) {
+    // when this area may go to another stream: after this launch if it is an eager one, never if it
+    // is part of a capture (the graph may be replayed at any time)
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    SS_CUDA(cudaStreamIsCapturing(stream, &capture));
+    std::lock_guard<std::mutex> lock(dev->split_mu);
+    if (capture != cudaStreamCaptureStatusNone) {
+      split_area->pinned = true;
+    } else {
+      SS_CUDA(cudaEventRecord(split_area->done, stream));
+      split_area->used = true;
+    }
+  }
   return SS_OK;
 }
 
@@ -552,21 +618,31 @@ int launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   Choice c = choose(a, dev->sms, true);
   // the tile-sum area is made on the first launch that wants it; a launch that cannot have it (a
   // stream capture before any such launch, no memory) takes the whole-tile schedule
-  if (c.split && !split_workspace(dev, stream)) c = choose(a, dev->sms, false);
+  DeviceInfo::SplitArea* area = c.split ? split_workspace(dev, stream, true) : nullptr;
+  if (c.split && !area) c = choose(a, dev->sms, false);
+  int rc;
   switch (c.nt) {
-    case 128: return launch_pair_nt<128, 2>(a, dev, 0, stream, 0, c.split);
-    case 192: return launch_pair_nt<192, 2>(a, dev, 1, stream, c.res_stages, c.split);
-    case 224: return launch_pair_nt<224, 2>(a, dev, 2, stream, c.res_stages, c.split);
-    case 240: return launch_pair_nt<240, 2>(a, dev, 3, stream, 0, c.split);
-    default:  return launch_pair_nt<256, 2>(a, dev, 4, stream, 0, c.split);
+    case 128: rc = launch_pair_nt<128, 2>(a, dev, 0, stream, 0, c.split); break;
+    case 192: rc = launch_pair_nt<192, 2>(a, dev, 1, stream, c.res_stages, c.split); break;
+    case 224: rc = launch_pair_nt<224, 2>(a, dev, 2, stream, c.res_stages, c.split); break;
+    case 240: rc = launch_pair_nt<240, 2>(a, dev, 3, stream, 0, c.split); break;
+    default:  rc = launch_pair_nt<256, 2>(a, dev, 4, stream, 0, c.split); break;
   }
+  if (area) {
+    std::lock_guard<std::mutex> lock(dev->split_mu);
+    --area->claims;
+  }
+  return rc;
 }
+
+long long split_launch_count() { return g_split_launches.load(std::memory_order_relaxed); }
 
 int reset_split_workspace() {
   DeviceInfo* dev = device_info();
   SS_REQUIRE(dev, SS_E_CUDA, "no current CUDA device");
-  if (!dev->split_ready.load(std::memory_order_acquire)) return SS_OK;
-  SS_CUDA(cudaMemset(dev->split_sum, 0, dev->split_bytes));
+  std::lock_guard<std::mutex> lock(dev->split_mu);
+  if (!dev->split_pool) return SS_OK;
+  SS_CUDA(cudaMemset(dev->split_pool, 0, dev->split_bytes * DeviceInfo::kSplitAreas));
   SS_CUDA(cudaDeviceSynchronize());
   return SS_OK;
 }

@@ -131,6 +131,17 @@ def test_large_token_tiles_full_height(backend, oracle, oracle_c, tile):
     assert backend.device_status() == 0
 
 
+_CAPTURE_STREAM = []
+
+
+def _capture_stream():
+    # one stream for all captures of this module: the library hands its split-schedule areas to at
+    # most four streams per device
+    if not _CAPTURE_STREAM:
+        _CAPTURE_STREAM.append(torch.cuda.Stream())
+    return _CAPTURE_STREAM[0]
+
+
 @pytest.mark.parametrize("tile", [0, 128, 192, 224, 240, 256])
 @pytest.mark.parametrize("mode,m,k,n", [(6, 666, 2432, 2304), (8, 256, 3072, 1024), (4, 700, 1152, 5000), (6, 100, 9728, 304)])
 def test_split_schedule_is_exact(backend, oracle, oracle_c, tile, mode, m, k, n):
@@ -145,6 +156,7 @@ def test_split_schedule_is_exact(backend, oracle, oracle_c, tile, mode, m, k, n)
     pitch = -(-n // 8) * 8
     lib = backend.library()
     with option(backend, "split", 1), option(backend, "token_tile", tile), option(backend, "resident", 0):
+        launches = backend.get_option("split_launches")
         for _ in range(3):
             wide = torch.full((m, pitch + 8), float("nan"), dtype=torch.bfloat16, device=DEV)
             check(backend, lib.ss_gemm_run(ptr(q), ptr(packed), ptr(meta), ptr(sa), ptr(sw), ptr(bias), None, 0, ptr(wide),
@@ -154,15 +166,21 @@ def test_split_schedule_is_exact(backend, oracle, oracle_c, tile, mode, m, k, n)
                 assert torch.isnan(wide[:, n:].float()).all()
             else:
                 assert np.array_equal(bits(wide[:, :n]), expect)       # unaligned n: the direct-store form ran
+        assert backend.get_option("split_launches") == launches + (3 if n % 8 == 0 else 0)
         if n % 8 == 0:
             out = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
-            side = torch.cuda.Stream()
+            side = _capture_stream()
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
+                # one launch outside the capture: a stream's split area is made by its first such launch
+                check(backend, lib.ss_gemm_run(ptr(q), ptr(packed), ptr(meta), ptr(sa), ptr(sw), ptr(bias), None, 0, ptr(out),
+                                               n, m, n, q.shape[0], packed.shape[0], q.shape[1], stream()))
+                before = backend.get_option("split_launches")
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
+                with torch.cuda.graph(graph, stream=side):
                     check(backend, lib.ss_gemm_run(ptr(q), ptr(packed), ptr(meta), ptr(sa), ptr(sw), ptr(bias), None, 0, ptr(out),
                                                    n, m, n, q.shape[0], packed.shape[0], q.shape[1], stream()))
+            assert backend.get_option("split_launches") == before + 1      # the captured launch is a split one
             torch.cuda.current_stream().wait_stream(side)
             for _ in range(3):
                 out.fill_(float("nan"))
@@ -181,6 +199,24 @@ def test_split_schedule_chosen_by_the_cost_model(backend, oracle, oracle_c):
     args = (dev(case["q"]), dev(case["packed"]), dev(case["meta_b200"], torch.int32), dev(case["sa"]), dev(case["scales"]),
             dev(case["bias"]), m, n)
     assert np.array_equal(bits(c_gemm_run(backend, *args)), expect)
+    # a launch the cost model gives the split schedule (100 tiles of 76 stages on 74 clusters), at a
+    # size the CPU oracle would take minutes for: seeded random operands, and the bits must equal
+    # those of the whole-tile schedule, whose results the other tests pin to the oracle
+    m2, n2, pk2 = 2048, 2432, 13056
+    gen = torch.Generator(device=DEV).manual_seed(11)
+    q2 = torch.randint(-127, 128, (m2, pk2), dtype=torch.int8, device=DEV, generator=gen)
+    packed2 = torch.randint(-127, 128, (n2, pk2 // 2), dtype=torch.int8, device=DEV, generator=gen)
+    meta2 = torch.full((n2 * pk2 // 32,), 0x44444444, dtype=torch.int32, device=DEV)       # positions 0 and 1 of every group of four
+    sa2 = torch.rand(m2, device=DEV, generator=gen) + 0.5
+    sw2 = torch.rand(n2, device=DEV, generator=gen) * 1e-3 + 1e-4
+    bias2 = torch.randn(n2, device=DEV, generator=gen)
+    launches = backend.get_option("split_launches")
+    auto = c_gemm_run(backend, q2, packed2, meta2, sa2, sw2, bias2, m2, n2)
+    assert backend.get_option("split_launches") == launches + 1
+    with option(backend, "split", 0):
+        whole = c_gemm_run(backend, q2, packed2, meta2, sa2, sw2, bias2, m2, n2)
+    assert backend.get_option("split_launches") == launches + 1
+    assert np.array_equal(bits(auto), bits(whole))
     with option(backend, "split", 0):
         assert np.array_equal(bits(c_gemm_run(backend, *args)), expect)
     assert backend.device_status() == 0
