@@ -1,23 +1,28 @@
-// CTA-pair variant of the sparse GEMM (tcgen05 cta_group::2).  Included by ss_gemm.cu inside
-// namespace ss::{anonymous}, after KernelArgs, smem_desc and store_chunk.
+// The sparse GEMM kernel: persistent clusters of two CTAs (tcgen05 cta_group::2).  Included by
+// ss_gemm.cu inside namespace ss::{anonymous}, after KernelArgs, smem_desc and store_chunk.
 //
-// Why a pair: the single-CTA kernel is bound by shared-memory bandwidth, not by the tensor
-// pipe.  A K=64 sparse INT8 MMA of M=128 x N reads 4 KB of A and 64*N bytes of B from shared
-// memory, and TMA wrote the same bytes there a moment earlier; at 128 B/clk for reads and writes
-// together that is 2*(5 KB + 64*N) / 128 cycles against N/2 cycles of tensor work (36 % of the
-// tensor peak at N = 192).  With cta_group::2 the two CTAs of a cluster compute 256 channels x N
-// tokens together: each CTA stores and reads its own 128 channel rows of A and only HALF of the
-// token rows of B (the hardware hands each half to the peer SM), which halves the dominant B
-// traffic (61 % at N = 256, 58 % at N = 224).  No multicast load is involved.
+// Why a pair: the two CTAs of a cluster compute 256 channels x N tokens together; each CTA loads,
+// stores and reads its own 128 channel rows of A (compressed weights + metadata) and only HALF of
+// the token rows of B (the hardware hands each half to the peer SM), which halves the dominant
+// activation traffic per SM and per MMA.  No multicast load is involved.  What bounds the kernel is
+// measured, not assumed: first the two single threads that drive the pipeline (TMA issue, MMA
+// issue, commits), now the round trip of the four-stage ring; see the diagnostics entry
+// ss_micro_pair_rate and the counters a -DSS_TIMELINE build keeps.
+//
+// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer (rank 0 only; also allocates TMEM), warps
+// 2..9 epilogue (two per TMEM lane quadrant), warp 10 metadata copier (streaming form, rank 0).
 //
 // Protocol (rank = %cluster_ctarank):
 //   full[s]      lives in rank 0 only.  Rank 0's producer posts the byte count of BOTH CTAs'
 //                loads; both producers issue their loads with the cta_group::2 form, which
-//                credits completion to rank 0's barrier.
+//                credits completion to rank 0's barrier; with a metadata warp its commit is the
+//                barrier's second arrival.
 //   empty[s]     one copy per CTA; the MMA thread (rank 0) commits with a 2-CTA multicast so
 //                both producers see the stage free at the same time.
 //   acc_full[b]  one copy per CTA, multicast commit; acc_empty[b] lives in rank 0 and counts the
-//                8 epilogue warps of the pair (rank 1 arrives through shared::cluster).
+//                16 epilogue warps of the pair (rank 1 arrives through shared::cluster).
+// Every wait on these barriers is bounded (ptx::mbar_wait): a wait that runs out records the role
+// in the device status word and the role winds down.
 #pragma once
 
 #ifndef SS_PAIR_EPI_WARPS
