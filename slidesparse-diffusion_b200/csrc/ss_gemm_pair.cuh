@@ -4,8 +4,11 @@
 // Why a pair: the two CTAs of a cluster compute 256 channels x N tokens together; each CTA loads,
 // stores and reads its own 128 channel rows of A (compressed weights + metadata) and only HALF of
 // the token rows of B (the hardware hands each half to the peer SM), which halves the dominant
-// activation traffic per SM and per MMA.  No multicast load is involved.  What bounds the kernel is
-// measured, not assumed: first the two single threads that drive the pipeline (TMA issue, MMA
+// activation traffic per SM and per MMA.  That matters because a single CTA's sparse INT8 MMA is
+// bound by the tensor core's 128 B/clk shared-memory read path, not by the tensor pipe (measured:
+// ss_micro_mma_rate settles at 127.5 operand bytes per clock whatever N is; A is half as wide after
+// compression, B is not).  No multicast load is involved.  What bounds the pair kernel is measured
+// too, not assumed: first the two single threads that drive the pipeline (TMA issue, MMA
 // issue, commits), now the round trip of the four-stage ring; see the diagnostics entry
 // ss_micro_pair_rate and the counters a -DSS_TIMELINE build keeps.
 //
