@@ -305,6 +305,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
                : "memory");
 }
+// The same store with an L2 eviction-priority hint: evict_first, for outputs far larger than L2,
+// whose lines would otherwise push the operands out while they wait for their write-back.
+__device__ __forceinline__ void tma_store_2d_evict_first(const CUtensorMap* map, const void* src, int x, int y) {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until at most N of this thread's bulk groups still have to read their shared-memory source.
 template <int N>

@@ -738,6 +738,8 @@ sparse_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             } else if constexpr (MODE == kOutBf16TmaPeers) {
               // the same staged tile goes to this GPU's and every peer's gathered output
               for (int g = 0; g < args.peer_count; ++g) ptx::tma_store_2d(&peers.m[g], stage, ch_w, tok0 + c * 32);
+            } else if (args.out_evict_first) {
+              ptx::tma_store_2d_evict_first(dst, stage, ch_w, tok0 + c * 32);
             } else {
               ptx::tma_store_2d(dst, stage, ch_w, tok0 + c * 32);
             }
