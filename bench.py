@@ -59,7 +59,7 @@ SAMPLE_TOKENS = 48            # rows per projection in the CPU sample (M = 1536 
 # output size (each output byte is written once; part of it is still in L2 when the kernel's
 # counters stop) = 116.6 / 161.9 / 158.3 MB against 116.0 / 149.1 / 123.9 MB algorithmic; the bench
 # scales the average algorithmic bytes per launch of its step by it
-TRAFFIC_OVER_ALGORITHMIC = (116.6 + 161.9 + 158.3) / (116.0 + 149.1 + 123.9)
+TRAFFIC_OVER_ALGORITHMIC = (116.1 + 151.4 + 158.1) / (116.0 + 149.1 + 123.9)
 
 
 def logical_ops(tokens=TOKENS):
