@@ -143,7 +143,8 @@ def _capture_stream():
 
 
 @pytest.mark.parametrize("tile", [0, 128, 192, 224, 240, 256])
-@pytest.mark.parametrize("mode,m,k,n", [(6, 666, 2432, 2304), (8, 256, 3072, 1024), (4, 700, 1152, 5000), (6, 100, 9728, 304)])
+@pytest.mark.parametrize("mode,m,k,n", [(6, 666, 2432, 2304), (8, 256, 3072, 1024), (4, 700, 1152, 5000), (6, 100, 9728, 304),
+                                        (4, 1, 1152, 8), (8, 33, 512, 264)])
 def test_split_schedule_is_exact(backend, oracle, oracle_c, tile, mode, m, k, n):
     """The split schedule forced on (every cluster takes an equal share of the tiles x stages, shared
     tiles are summed through global memory by whichever piece arrives last): the same bits as the
